@@ -44,6 +44,17 @@ SWEEP_SHAPES = [(4096, 11008), (11008, 4096), (4096, 14336), (14336, 4096)]
 SWEEP_BATCHES = [1, 16, 128, 4096, 16384]
 
 
+def stack_config(blocks: int, tokens: int, world: int) -> dict:
+    """`config` of the default workload, the same words on both arms."""
+
+    return {
+        "workload": f"converted SwiGLU MLP stack: {blocks} blocks, d={D_MODEL}, ffn={D_FFN}, "
+                    f"{tokens} tokens per GPU, all {3 * blocks} matrices binary, evidence all-reduce per step",
+        "tokens_per_gpu": tokens, "parallelism": f"dp{world}",
+        "l2": "inputs larger than L2 (134 MB of activations per step, two rotating batches)",
+    }
+
+
 def peaks() -> dict:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -63,10 +74,13 @@ class SwiGLU(nn.Module):
         self.gate = nn.Linear(dim, ffn, bias=False, device=device)
         self.up = nn.Linear(dim, ffn, bias=False, device=device)
         self.down = nn.Linear(ffn, dim, bias=False, device=device)
+        # a module, not F.silu: convert(activations=True) swaps it for the packed SiLU, which
+        # keeps an int8 derivative tape instead of the bf16 pre-activation
+        self.act = nn.SiLU()
 
     def forward(self, x):
         h = F.rms_norm(x, (x.shape[-1],))
-        return x + self.down(F.silu(self.gate(h)) * self.up(h))
+        return x + self.down(self.act(self.gate(h)) * self.up(h))
 
 
 class Stack(nn.Module):
@@ -177,11 +191,6 @@ def run_ours(args) -> dict:
     if world > 1:
         import torch.distributed as dist
 
-        # The persistent GEMMs leave eight SMs to the evidence all-reduce that runs beside them
-        # (read once, when the library plans its first GEMM): without it NCCL's blocks wait for
-        # a GEMM to end and the next GEMM's blocks then start late.  8 GPUs: 901.8 -> 946.7 k
-        # tokens/s (16 SMs: 933.8 k; limiting NCCL's blocks instead: 861.4 k).
-        os.environ.setdefault("QSTE_B200_RESERVED_SMS", "8")
         dist.init_process_group("nccl", device_id=device)
     tokens = args.tokens or TOKENS
     blocks = args.blocks or BLOCKS
@@ -189,7 +198,11 @@ def run_ours(args) -> dict:
     torch.manual_seed(1234)  # same weights on every rank
     model = Stack(blocks, D_MODEL, D_FFN, device)
     qste.convert(model, include=["blocks.*.gate", "blocks.*.up", "blocks.*.down"])
-    reducer = qdist.mean_evidence(overlap=True) if world > 1 else None
+    # The backward GEMMs (only those: no collective is in flight during forward) leave a few SMs
+    # to the evidence all-reduce that runs beside them; without that NCCL's blocks wait for a
+    # GEMM to end and the next GEMM's blocks then start late.
+    reducer = qdist.mean_evidence(overlap=True, reserve_sms=args.reserve if args.reserve >= 0 else None) \
+        if world > 1 else None
     coordinates = qste.QSTEOptimizer(model, gradient_reducer=reducer if reducer else False, async_update=True)
     floats = list(qste.continuous_parameters(model))
     host_optimizer = torch.optim.AdamW(floats, lr=1e-3, fused=True)
@@ -282,12 +295,7 @@ def run_ours(args) -> dict:
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * seconds / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (N(0,1) activations, random-init weights)",
-        "config": {
-            "workload": f"converted SwiGLU MLP stack: {blocks} blocks, d={D_MODEL}, ffn={D_FFN}, "
-                        f"{tokens} tokens per GPU, all {3 * blocks} matrices binary, evidence all-reduce per step",
-            "tokens_per_gpu": tokens, "parallelism": f"dp{world}",
-            "l2": "inputs larger than L2 (134 MB of activations per step, two rotating batches)",
-        },
+        "config": stack_config(blocks, tokens, world),
         "e2e": {"value": world * tokens * args.steps / e2e_seconds, "unit": "tokens/s",
                 "h2d_bytes_per_step": staging[0].numel() * staging[0].element_size(), "d2h_bytes_per_step": 4},
         "gpu_launches": launches,
@@ -306,7 +314,7 @@ def run_ours(args) -> dict:
             # the per-kernel table and the CPU baseline belong to the one-GPU line; at N > 1 the
             # other ranks would only wait for them
             result["kernels"] = kernel_breakdown(device, tokens)
-            result["cpu_baseline"] = cpu_baseline(steps=2, warmup=1)
+            result["cpu_baseline"] = cpu_baseline(tokens)
     if world > 1:
         import torch.distributed as dist
 
@@ -504,10 +512,11 @@ def _cpu_kernels():
 
 class CpuBinaryLinear:
     """One converted Linear on the CPU through the reference's kernels, following
-    src/qste/functional.py:153-194 and src/qste/optim.py:156-178 call for call."""
+    src/qste/functional.py:153-194 and src/qste/optim.py:156-178 call for call.  `clock`
+    collects the seconds spent per kind of call."""
 
-    def __init__(self, k, rows, columns, generator, index):
-        self.k, self.rows, self.columns, self.index = k, rows, columns, index
+    def __init__(self, k, rows, columns, generator, index, clock):
+        self.k, self.rows, self.columns, self.index, self.clock = k, rows, columns, index, clock
         self.coordinate = torch.randint(-127, 128, (rows, columns), generator=generator, dtype=torch.int32).to(torch.int8)
         self.packed = k.pack_coordinate(self.coordinate)
         self.scale = torch.full((rows,), 0.02)
@@ -517,38 +526,52 @@ class CpuBinaryLinear:
         self.row_v = torch.zeros(rows, dtype=torch.float16)
         self.col_v = torch.zeros(columns, dtype=torch.float16)
 
+    def timed(self, kind, call, *args):
+        begin = time.perf_counter()
+        result = call(*args)
+        self.clock[kind] = self.clock.get(kind, 0.0) + time.perf_counter() - begin
+        return result
+
     def forward(self, x):
-        y = self.k.packed_linear_affine(x, self.packed, self.scale, None, self.columns)
-        bits, offset, scale = self.k.pack_affine_rows(x)
-        self.saved = (bits, offset, scale)
+        y = self.timed("gemm", self.k.packed_linear_affine, x, self.packed, self.scale, None, self.columns)
+        self.saved = self.timed("pack_affine_rows", self.k.pack_affine_rows, x)
         return y
 
     def backward(self, dy, step):
         bits, offset, act_scale = self.saved
-        dx = self.k.packed_transpose(dy, self.packed, self.columns, self.scale)
-        evidence = self.k.evidence_from_packed(dy, bits, self.columns, act_scale)
+        dx = self.timed("gemm", self.k.packed_transpose, dy, self.packed, self.columns, self.scale)
+        evidence = self.timed("gemm", self.k.evidence_from_packed, dy, bits, self.columns, act_scale)
+        begin = time.perf_counter()
         evidence.add_(torch.mv(dy.t(), offset).unsqueeze(1))
         g_scale = self.k.packed_row_inner(evidence, self.packed, self.columns)
         evidence.mul_(self.scale.unsqueeze(1))
-        flips = self.k.coordinate_update(evidence, self.coordinate, self.packed, self.moment_q, self.moment_scale,
-                                         self.row_v, self.col_v, 0.9, 0.99, 2.0, 1.0, 256, 1 + 1_000_003 * self.index, step)
+        self.clock["evidence_epilogue"] = self.clock.get("evidence_epilogue", 0.0) + time.perf_counter() - begin
+        flips = self.timed("coordinate_update", self.k.coordinate_update, evidence, self.coordinate, self.packed,
+                           self.moment_q, self.moment_scale, self.row_v, self.col_v, 0.9, 0.99, 2.0, 1.0, 256,
+                           1 + 1_000_003 * self.index, step)
         return dx, g_scale, int(flips)
 
 
-def cpu_block_seconds(tokens: int, steps: int, warmup: int):
-    """Seconds per training step of ONE SwiGLU block on the CPU (forward, backward,
-    three coordinate updates)."""
+def cpu_block_steps(tokens: int, steps: int, warmup: int, budget_s: float | None = None,
+                    dim: int = D_MODEL, ffn: int = D_FFN):
+    """Training steps of ONE SwiGLU block on the CPU (forward, backward, three coordinate
+    updates), each timed.  Runs `warmup + steps` steps, or as many as finish inside `budget_s`
+    seconds (at least one).  Returns (seconds of every timed step, steps discarded as warm-up,
+    seconds per kind of call summed over the timed steps, kind)."""
 
     k, kind = _cpu_kernels()
     generator = torch.Generator().manual_seed(5)
-    gate = CpuBinaryLinear(k, D_FFN, D_MODEL, generator, 0)
-    up = CpuBinaryLinear(k, D_FFN, D_MODEL, generator, 1)
-    down = CpuBinaryLinear(k, D_MODEL, D_FFN, generator, 2)
-    x = torch.randn(tokens, D_MODEL, generator=generator)
-    times = []
+    clock: dict = {}
+    gate = CpuBinaryLinear(k, ffn, dim, generator, 0, clock)
+    up = CpuBinaryLinear(k, ffn, dim, generator, 1, clock)
+    down = CpuBinaryLinear(k, dim, ffn, generator, 2, clock)
+    x = torch.randn(tokens, dim, generator=generator)
+    times, clocks = [], []
+    started = time.perf_counter()
     for number in range(warmup + steps):
+        clock.clear()
         begin = time.perf_counter()
-        h = F.rms_norm(x, (D_MODEL,))
+        h = F.rms_norm(x, (dim,))
         g, u = gate.forward(h), up.forward(h)
         s = torch.sigmoid(g)
         a = g * s
@@ -559,21 +582,45 @@ def cpu_block_seconds(tokens: int, steps: int, warmup: int):
         dg = dmid * u * (s * (1 + g * (1 - s)))
         up.backward(du, number)
         gate.backward(dg, number)
-        if number >= warmup:
-            times.append(time.perf_counter() - begin)
-    return statistics.median(times), kind
+        seconds = time.perf_counter() - begin
+        clock["harness_elementwise"] = seconds - sum(clock.values())
+        times.append(seconds)
+        clocks.append(dict(clock))
+        spent = time.perf_counter() - started
+        if budget_s is not None and spent + 1.2 * seconds > budget_s:
+            break
+    # the first step pays for first-touch page faults of several GB: it is the warm-up whenever
+    # there is a second one
+    discarded = min(warmup, len(times) - 1)
+    times, clocks = times[discarded:], clocks[discarded:]
+    split = {key: sum(c.get(key, 0.0) for c in clocks) / len(clocks) for key in clocks[0]}
+    return times, discarded, split, kind
 
 
-def cpu_baseline(steps: int, warmup: int, tokens: int = 256) -> dict:
-    seconds, kind = cpu_block_seconds(tokens, steps, warmup)
+def cpu_baseline(tokens: int = TOKENS) -> dict:
+    """The reference's CPU kernels on ONE SwiGLU block at the workload's full token count, one
+    step, measured not extrapolated; tokens/s of the 8-block stack = tokens / (8 x block time)."""
+
+    times, _, split, kind = cpu_block_steps(tokens, 1, 0)
+    seconds = statistics.median(times)
     return {"value": tokens / (seconds * BLOCKS), "unit": "tokens/s", "cores": torch.get_num_threads(),
             "host_cpus": os.cpu_count(), "kind": kind,
-            "sample": f"one SwiGLU block (d={D_MODEL}, ffn={D_FFN}) x {tokens} tokens, fp32, forward + backward + "
-                      f"3 coordinate updates, median of {steps}; tokens/s = tokens / ({BLOCKS} blocks x block time)",
-            "seconds_per_block_step": seconds}
+            "sample": f"one SwiGLU block (d={D_MODEL}, ffn={D_FFN}) x {tokens} tokens (the workload's own count), fp32, "
+                      f"forward + backward + 3 coordinate updates, 1 step; tokens/s = tokens / ({BLOCKS} blocks x block time)",
+            "seconds_per_block_step": seconds,
+            "seconds_by_call": {key: round(value, 3) for key, value in split.items()}}
 
 
 def run_reference(args) -> dict:
+    """The reference's own CPU kernels on the workload of the repo arm.
+
+    A step of the 8-block stack is eight identical blocks, so ONE block is timed, at the
+    config's full token count (the three coordinate updates of a block cost the same whatever
+    the batch, so a smaller batch would understate the CPU's tokens/s), and the stack's
+    tokens/s is tokens / (8 x block time).  A block step takes tens of seconds on the host
+    cores: the arm runs the steps that fit its time budget (QSTE_BENCH_REFERENCE_BUDGET_S,
+    default 150 s), at least one, and reports how many it timed in `steps`."""
+
     if int(os.environ.get("RANK", "0")) != 0:
         return {}
     # torchrun sets OMP_NUM_THREADS=1 for its workers; this arm is the reference on all host cores
@@ -581,18 +628,26 @@ def run_reference(args) -> dict:
         torch.set_num_threads(max(torch.get_num_threads(), len(os.sched_getaffinity(0))))
     except (AttributeError, RuntimeError):
         pass
-    tokens = 256
-    seconds, kind = cpu_block_seconds(tokens, max(1, args.steps), max(0, args.warmup))
+    tokens = args.tokens or TOKENS
+    budget = float(os.environ.get("QSTE_BENCH_REFERENCE_BUDGET_S", "150"))
+    times, discarded, split, kind = cpu_block_steps(tokens, max(1, args.steps), max(0, args.warmup), budget_s=budget)
+    seconds = statistics.median(times)
     value = tokens / (seconds * BLOCKS)
     return {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * seconds * BLOCKS, "higher_is_better": True, "scaling": "weak",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": len(times), "warmup": discarded,
+        "steps_requested": args.steps, "warmup_requested": args.warmup,
+        "ms_per_step": 1e3 * seconds, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"converted SwiGLU MLP stack: {BLOCKS} blocks, d={D_MODEL}, ffn={D_FFN} "
-                               f"(CPU sample: one block x {tokens} tokens per step, scaled to {BLOCKS} blocks)"},
+        "config": dict(stack_config(BLOCKS, tokens, 1),
+                       cpu_sample=f"the CPU arm times ONE of the {BLOCKS} identical blocks per step, at the full {tokens} "
+                                  f"tokens: ms_per_step is that block step (median of {len(times)} timed inside a "
+                                  f"{budget:.0f} s budget) and value = tokens / ({BLOCKS} x block time)"),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
-                         "sample": f"one SwiGLU block x {tokens} tokens per step, fp32, all host threads torch uses"},
+                         "sample": f"one SwiGLU block x {tokens} tokens per step, fp32, all host threads torch uses; "
+                                   f"{len(times)} timed step(s) after {discarded} warm-up",
+                         "seconds_per_block_step": seconds,
+                         "seconds_by_call": {key: round(v, 3) for key, v in split.items()}},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
 
@@ -695,11 +750,11 @@ def run_kernel(args) -> dict:
     m, k, n = args.tokens or TOKENS, D_MODEL, D_FFN
     x, bits, scale = _gemm_inputs(device, m, k, n)
     generator = torch.Generator(device=device).manual_seed(3)
-    if args.kernel in ("dx", "evidence"):
+    if args.kernel in ("dx", "evidence", "backward"):
         dy = torch.randn(m, n, device=device, dtype=torch.bfloat16, generator=generator)
         act_bits, act_offset, act_scale = kernels.pack_affine_rows(x)
         aux = torch.stack((act_offset, act_scale))
-    if args.kernel == "update":
+    if args.kernel in ("update", "pack_coordinate", "row_inner"):
         coordinate = torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8, generator=generator)
         packed = kernels.pack_coordinate(coordinate)
         moment_q = torch.zeros_like(coordinate)
@@ -712,7 +767,10 @@ def run_kernel(args) -> dict:
         "forward": lambda: kernels.packed_linear_affine(x, bits, scale, None, k),
         "dx": lambda: kernels.packed_transpose(dy, bits, k, scale),
         "evidence": lambda: kernels.linear_backward_evidence(dy, act_bits, aux, k, bits, scale),
+        "backward": lambda: kernels.linear_backward(dy, bits, scale, k, act_bits, aux),
         "pack": lambda: kernels.pack_affine_rows(x),
+        "pack_coordinate": lambda: kernels.pack_coordinate(coordinate),
+        "row_inner": lambda: kernels.packed_row_inner(evidence, packed, k),
         "update": lambda: kernels.coordinate_update(
             evidence, coordinate, packed, moment_q, moment_scale, row_v, col_v, beta1=0.9, beta2=0.99,
             update_clip=2.0, coordinate_lr=1.0, block_size=256, seed=1, step=0, flips=flips),
@@ -732,11 +790,13 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="mlp_stack", choices=["mlp_stack", "gemm_sweep", "kernel"])
-    parser.add_argument("--kernel", default="forward", choices=["forward", "dx", "evidence", "pack", "update"],
+    parser.add_argument("--kernel", default="forward", choices=["forward", "dx", "evidence", "backward", "pack", "pack_coordinate", "row_inner", "update"],
                         help="with --workload kernel: which kernel to launch")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the per-kernel roofline section and the CPU baseline (profiling runs)")
     parser.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default 16384)")
+    parser.add_argument("--reserve", type=int, default=-1,
+                        help="SMs the backward GEMMs leave to the all-reduce at N > 1 (default: the library's, 8)")
     parser.add_argument("--blocks", type=int, default=0, help="SwiGLU blocks (default 8)")
     args = parser.parse_args()
     if args.impl == "reference":

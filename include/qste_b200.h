@@ -65,10 +65,38 @@ const char* qste_b200_status_string(int status);
 const char* qste_b200_last_cuda_error(void);
 /* Number of kernels this library has launched in this process so far. */
 unsigned long long qste_b200_launch_count(void);
-/* Device-side wait diagnostics: kernels that wait on an mbarrier give up after a
- * bounded number of polls and add 1 to a counter in the workspace; projection and
- * optimizer calls that take a workspace leave that counter at workspace[0..7] as a
- * uint64.  The Python wrapper checks it in debug mode. */
+/* The tensor-core GEMMs are persistent kernels with one block per SM.  A collective that runs
+ * beside them on another stream (the evidence all-reduce of data-parallel training) finds no
+ * free SM until a GEMM ends.  This sets how many SMs the GEMMs launched FROM THE CALLING THREAD
+ * leave free from now on (0 = none, the default; the environment variable
+ * QSTE_B200_RESERVED_SMS gives a thread's initial value) and returns the previous setting.
+ * It changes the GEMMs' grid and so the size *_workspace() reports: set it before the
+ * workspace query of the call it is meant for.  No counterpart in the reference, whose GEMMs
+ * are cuBLAS calls. */
+int qste_b200_set_reserved_sms(int count);
+
+/* ---- workspaces --------------------------------------------------------------
+ * A workspace is caller-owned device memory, 256-byte aligned, at least as large as the
+ * matching *_workspace() reports, and used by one call at a time (one workspace per stream).
+ * Its first 256 bytes are a header that the library reads and updates across calls; the caller
+ * must ZERO THE HEADER ONCE, before the first call that uses the buffer (cudaMemset of 256
+ * bytes), and carry it over if it replaces the buffer by a larger one.  Layout (all uint64):
+ *   bytes   0..7    number of bounded device-side waits that gave up (0 in a healthy run; a
+ *                   GEMM whose wait gave up returns QSTE_OK all the same, and its output is
+ *                   incomplete: check this counter wherever the stream is synchronised anyway)
+ *   bytes   8..15   flip count of the last coordinate_update
+ *   bytes  64..191  per-role cycle counters of the GEMM (filled when QSTE_B200_TC_PROFILE is set)
+ *   bytes 192..199  the GEMM's work-item counter, zero between launches: a non-zero start makes a
+ *                   launch skip tiles, which is why the header must start zeroed
+ *   bytes 200..207  where the first wait gave up: source line << 32 | block << 16 | thread
+ * The rest is scratch with no meaning between calls.
+ *
+ * Process-wide state the library keeps (everything else lives in caller memory): per-device
+ * caches of the SM count, the compute capability, "shared-memory attribute set" flags and the
+ * resident-cluster capacity of the pair kernel (written once each, identical values from any
+ * thread); the driver entry point of cuTensorMapEncodeTiled; a launch counter; per-thread: the
+ * last CUDA error text and the reserved-SM setting.  The environment switches QSTE_B200_TC_*
+ * (test and profiling only) are read once, at the first GEMM of the process. */
 
 /* ---- packing --------------------------------------------------------------- */
 
@@ -161,6 +189,21 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
                               const uint8_t* act_bits, const float* aux, void* grad_input,
                               int grad_input_dtype, float* evidence, float* g_scale, float* g_bias,
                               void* workspace, size_t workspace_bytes, qste_stream_t stream);
+
+/* qste_b200_linear_backward for a caller that overlaps the backward with work on another
+ * stream.  The evidence product runs first; when `evidence_ready` (a cudaEvent_t the caller
+ * created, or NULL) is given it is recorded on `stream` as soon as evidence, g_scale and g_bias
+ * are complete, before the dX product is enqueued, so an all-reduce or a coordinate update on a
+ * second stream can wait for that event and run beside dX.  grad_input may be NULL: dX is then
+ * not computed at all (a layer whose input needs no gradient).
+ * Reference: QSTELinearFn.backward, src/qste/functional.py:173-194 together with the reducer
+ * call of QSTEOptimizer._apply, src/qste/optim.py:156-178, which it lets start early. */
+int qste_b200_linear_backward_staged(const void* grad, int dtype, int64_t samples, int64_t rows,
+                                     const uint8_t* weight_bits, const float* weight_scale,
+                                     int64_t columns, const uint8_t* act_bits, const float* aux,
+                                     void* grad_input, int grad_input_dtype, float* evidence,
+                                     float* g_scale, float* g_bias, void* evidence_ready,
+                                     void* workspace, size_t workspace_bytes, qste_stream_t stream);
 
 /* out[r] = sum_c matrix[r, c] * sign[r, c], fp32.
  * Reference: kernels.packed_row_inner, loader.py:315-319, cpu.cpp:460-496. */

@@ -11,12 +11,16 @@ compiler cannot contract ``a*b+c`` into an FMA and the integer outputs depend on
 on IEEE fp32 arithmetic.  Like the loader's build, there is no ``-fopenmp``: the
 hand-written loops run on the calling thread and only ``at::mm`` is threaded.
 
-Usage:  python oracle/build_ref.py [/path/to/reference]
+Where the reference checkout is: the argument, else the environment variable
+QSTE_REFERENCE, else a directory named ``reference`` beside this repository.
+
+Usage:  python oracle/build_ref.py [path/to/reference]
 """
 
 from __future__ import annotations
 
 import importlib.util
+import os
 import subprocess
 import sys
 import sysconfig
@@ -24,11 +28,17 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref" / "qste_cpu.so"
-DEFAULT_REFERENCE = Path("/root/reference")
 
 
-def build(reference: Path = DEFAULT_REFERENCE, force: bool = False) -> Path | None:
-    source = reference / "src" / "qste" / "kernels" / "cpu.cpp"
+def reference_root() -> Path:
+    """The reference checkout: $QSTE_REFERENCE, else ``reference`` beside this repository."""
+
+    named = os.environ.get("QSTE_REFERENCE")
+    return Path(named) if named else HERE.parent.parent / "reference"
+
+
+def build(reference: Path | None = None, force: bool = False) -> Path | None:
+    source = (reference or reference_root()) / "src" / "qste" / "kernels" / "cpu.cpp"
     if not source.exists():
         return OUT if OUT.exists() else None
     if OUT.exists() and not force and OUT.stat().st_mtime >= source.stat().st_mtime:
@@ -66,5 +76,5 @@ def load():
 
 
 if __name__ == "__main__":
-    target = build(Path(sys.argv[1]) if len(sys.argv) > 1 else DEFAULT_REFERENCE, force=True)
+    target = build(Path(sys.argv[1]) if len(sys.argv) > 1 else None, force=True)
     print(target if target else "reference not present; nothing built")

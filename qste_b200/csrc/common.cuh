@@ -46,6 +46,8 @@ inline cudaStream_t as_stream(qste_stream_t stream) { return reinterpret_cast<cu
 
 // Number of SMs of the current device (cached per device id).
 int sm_count();
+// SMs the calling thread's persistent GEMMs leave free (qste_b200_set_reserved_sms).
+int reserved_sms();
 // QSTE_OK when the current device is compute capability 10.x.
 int check_arch();
 

@@ -1214,9 +1214,10 @@ TcPlan tc_plan(long long I, long long J, int kblocks_total) {
   static const bool never_tall = getenv("QSTE_B200_TC_SHORT") != nullptr;    // for A/B timing
   static const bool never_pair = getenv("QSTE_B200_TC_NOPAIR") != nullptr;
   static const bool never_split = getenv("QSTE_B200_TC_NOSPLIT") != nullptr;
-  // QSTE_B200_RESERVED_SMS=n: the persistent GEMMs leave n SMs alone, for a collective that runs
-  // beside them on another stream (its blocks cannot be placed while every SM holds a GEMM block)
-  static const int reserved = getenv("QSTE_B200_RESERVED_SMS") ? atoi(getenv("QSTE_B200_RESERVED_SMS")) : 0;
+  // the persistent GEMMs leave this many SMs alone, for a collective that runs beside them on
+  // another stream (its blocks cannot be placed while every SM holds a GEMM block); a per-thread
+  // setting, so the workspace query and the call that follows it in one thread see one value
+  const int reserved = reserved_sms();
   TcPlan plan;
   int sms = sm_count();
   if (reserved > 0 && reserved < sms - 8) sms -= reserved;

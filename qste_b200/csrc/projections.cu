@@ -237,7 +237,33 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
                               const uint8_t* act_bits, const float* aux, void* grad_input,
                               int grad_input_dtype, float* evidence, float* g_scale, float* g_bias,
                               void* workspace, size_t workspace_bytes, qste_stream_t stream) {
+  return qste_b200_linear_backward_staged(grad, dtype, samples, rows, weight_bits, weight_scale, columns, act_bits,
+                                          aux, grad_input, grad_input_dtype, evidence, g_scale, g_bias, nullptr,
+                                          workspace, workspace_bytes, stream);
+}
+
+// Marks "evidence, g_scale and g_bias are complete" on the stream for a caller that passed an event.
+static int mark_evidence_ready(void* event, cudaStream_t s) {
+  if (!event) return QSTE_OK;
+  const cudaError_t error = cudaEventRecord(static_cast<cudaEvent_t>(event), s);
+  if (error != cudaSuccess) { set_last_cuda_error(error, "cudaEventRecord(evidence_ready)"); return QSTE_ERR_CUDA; }
+  return QSTE_OK;
+}
+
+int qste_b200_linear_backward_staged(const void* grad, int dtype, int64_t samples, int64_t rows,
+                                     const uint8_t* weight_bits, const float* weight_scale, int64_t columns,
+                                     const uint8_t* act_bits, const float* aux, void* grad_input,
+                                     int grad_input_dtype, float* evidence, float* g_scale, float* g_bias,
+                                     void* evidence_ready, void* workspace, size_t workspace_bytes,
+                                     qste_stream_t stream) {
   if (samples < 0 || rows < 0 || columns < 0) return QSTE_ERR_SHAPE;
+  if (!grad_input) {
+    // nobody reads dX (the first layer of a model): the evidence side alone
+    const int status = qste_b200_linear_backward_evidence(grad, dtype, samples, rows, act_bits, aux, columns,
+                                                          weight_bits, weight_scale, evidence, g_scale, g_bias,
+                                                          QSTE_PATH_AUTO, workspace, workspace_bytes, stream);
+    return status != QSTE_OK ? status : mark_evidence_ready(evidence_ready, as_stream(stream));
+  }
   if (!valid_dtype(dtype) || !valid_dtype(grad_input_dtype)) return QSTE_ERR_DTYPE;
   if (!workspace || workspace_bytes < qste_b200_linear_backward_workspace(samples, rows, columns, dtype))
     return QSTE_ERR_WORKSPACE;
@@ -248,13 +274,15 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
                      tc_supported(TC_EVIDENCE, rows, columns, samples, dtype, grad, act_bits, evidence, QSTE_F32);
   if (!fused) {
     // any other combination: the two calls, one after the other, sharing the workspace
-    int status = qste_b200_packed_transpose(grad, dtype, samples, weight_bits, weight_scale, rows, columns,
-                                            grad_input, grad_input_dtype, QSTE_PATH_AUTO, workspace,
-                                            workspace_bytes, stream);
+    int status = qste_b200_linear_backward_evidence(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits,
+                                                    weight_scale, evidence, g_scale, g_bias, QSTE_PATH_AUTO,
+                                                    workspace, workspace_bytes, stream);
     if (status != QSTE_OK) return status;
-    return qste_b200_linear_backward_evidence(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits,
-                                              weight_scale, evidence, g_scale, g_bias, QSTE_PATH_AUTO,
-                                              workspace, workspace_bytes, stream);
+    status = mark_evidence_ready(evidence_ready, as_stream(stream));
+    if (status != QSTE_OK) return status;
+    return qste_b200_packed_transpose(grad, dtype, samples, weight_bits, weight_scale, rows, columns,
+                                      grad_input, grad_input_dtype, QSTE_PATH_AUTO, workspace,
+                                      workspace_bytes, stream);
   }
   cudaStream_t s = as_stream(stream);
   const BackwardLayout l = backward_layout(samples, rows, columns, dtype);
@@ -274,17 +302,8 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
     int status = prepare_rows(grad, aux, aux + samples, samples, rows, half_copy, row_unscale, row_cs, g_bias,
                               correction, base + l.sums, s);
     if (status != QSTE_OK) return status;
-    TcProblem dx = {};
-    dx.kind = TC_TRANSPOSE;
-    dx.a = grad; dx.a_dtype = dtype; dx.a_prepared = half_copy; dx.a_prepared_mult = nullptr;
-    dx.bits = weight_bits; dx.bit_pitch = pitch; dx.contraction_scale = weight_scale;
-    dx.row_scale = row_unscale;
-    dx.out = grad_input; dx.out_dtype = grad_input_dtype;
-    dx.I = samples; dx.J = columns; dx.K = rows;
-    dx.workspace = base + l.tc;
-    dx.diagnostics = static_cast<unsigned long long*>(workspace);
-    status = tc_run(dx, s);
-    if (status != QSTE_OK) return status;
+    // The evidence product goes first: whoever reduces or applies it on another stream (the
+    // all-reduce across ranks, the coordinate update) can start while dX is still being formed.
     TcProblem ev = {};
     ev.kind = TC_EVIDENCE;
     ev.a = grad; ev.a_dtype = dtype; ev.a_prepared = half_copy; ev.a_prepared_mult = nullptr;
@@ -294,7 +313,20 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
     ev.row_add = correction; ev.row_scale = weight_scale; ev.inner_bits = weight_bits; ev.inner_out = g_scale;
     ev.workspace = base + l.tc;
     ev.diagnostics = static_cast<unsigned long long*>(workspace);
-    return tc_run(ev, s);
+    status = tc_run(ev, s);
+    if (status != QSTE_OK) return status;
+    status = mark_evidence_ready(evidence_ready, s);
+    if (status != QSTE_OK) return status;
+    TcProblem dx = {};
+    dx.kind = TC_TRANSPOSE;
+    dx.a = grad; dx.a_dtype = dtype; dx.a_prepared = half_copy; dx.a_prepared_mult = nullptr;
+    dx.bits = weight_bits; dx.bit_pitch = pitch; dx.contraction_scale = weight_scale;
+    dx.row_scale = row_unscale;
+    dx.out = grad_input; dx.out_dtype = grad_input_dtype;
+    dx.I = samples; dx.J = columns; dx.K = rows;
+    dx.workspace = base + l.tc;
+    dx.diagnostics = static_cast<unsigned long long*>(workspace);
+    return tc_run(dx, s);
   }
 
   // one pass over dY: bias gradient, offset correction and the largest magnitude
@@ -306,17 +338,6 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
   status = tc_prepare_half(grad, samples * rows, amax_slot, a_mult, half_copy, s);
   if (status != QSTE_OK) return status;
 
-  TcProblem dx = {};
-  dx.kind = TC_TRANSPOSE;
-  dx.a = grad; dx.a_dtype = dtype; dx.a_prepared = half_copy; dx.a_prepared_mult = a_mult;
-  dx.bits = weight_bits; dx.bit_pitch = pitch; dx.contraction_scale = weight_scale;
-  dx.out = grad_input; dx.out_dtype = grad_input_dtype;
-  dx.I = samples; dx.J = columns; dx.K = rows;
-  dx.workspace = base + l.tc;
-  dx.diagnostics = static_cast<unsigned long long*>(workspace);
-  status = tc_run(dx, s);
-  if (status != QSTE_OK) return status;
-
   TcProblem ev = {};
   ev.kind = TC_EVIDENCE;
   ev.a = grad; ev.a_dtype = dtype; ev.a_prepared = half_copy; ev.a_prepared_mult = a_mult;
@@ -326,7 +347,20 @@ int qste_b200_linear_backward(const void* grad, int dtype, int64_t samples, int6
   ev.row_add = correction; ev.row_scale = weight_scale; ev.inner_bits = weight_bits; ev.inner_out = g_scale;
   ev.workspace = base + l.tc;
   ev.diagnostics = static_cast<unsigned long long*>(workspace);
-  return tc_run(ev, s);
+  status = tc_run(ev, s);
+  if (status != QSTE_OK) return status;
+  status = mark_evidence_ready(evidence_ready, s);
+  if (status != QSTE_OK) return status;
+
+  TcProblem dx = {};
+  dx.kind = TC_TRANSPOSE;
+  dx.a = grad; dx.a_dtype = dtype; dx.a_prepared = half_copy; dx.a_prepared_mult = a_mult;
+  dx.bits = weight_bits; dx.bit_pitch = pitch; dx.contraction_scale = weight_scale;
+  dx.out = grad_input; dx.out_dtype = grad_input_dtype;
+  dx.I = samples; dx.J = columns; dx.K = rows;
+  dx.workspace = base + l.tc;
+  dx.diagnostics = static_cast<unsigned long long*>(workspace);
+  return tc_run(dx, s);
 }
 
 }  // extern "C"

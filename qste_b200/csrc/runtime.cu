@@ -1,6 +1,7 @@
 // Library-wide helpers: status strings, last CUDA error, device queries.
 #include <atomic>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -16,6 +17,19 @@ void set_last_cuda_error(cudaError_t error, const char* where) {
 
 static std::atomic<unsigned long long> g_launches{0};
 void note_launches(int count) { g_launches.fetch_add((unsigned long long)count, std::memory_order_relaxed); }
+
+// SMs the persistent GEMMs of the calling thread leave free (see qste_b200_set_reserved_sms);
+// -1: not set yet, take QSTE_B200_RESERVED_SMS from the environment
+static thread_local int g_reserved_sms = -1;
+
+int reserved_sms() {
+  if (g_reserved_sms < 0) {
+    const char* text = getenv("QSTE_B200_RESERVED_SMS");
+    const int value = text ? atoi(text) : 0;
+    g_reserved_sms = value > 0 ? value : 0;
+  }
+  return g_reserved_sms;
+}
 
 int sm_count() {
   static int cached[64];
@@ -75,6 +89,12 @@ const char* qste_b200_status_string(int status) {
 }
 
 const char* qste_b200_last_cuda_error(void) { return qste::g_last_error; }
+
+int qste_b200_set_reserved_sms(int count) {
+  const int previous = qste::reserved_sms();
+  qste::g_reserved_sms = count > 0 ? count : 0;
+  return previous;
+}
 
 unsigned long long qste_b200_launch_count(void) { return qste::g_launches.load(std::memory_order_relaxed); }
 

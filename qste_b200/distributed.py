@@ -55,21 +55,63 @@ def _all_reduce(evidence: Tensor, group, average: bool, overlap: bool, join: boo
         # valid on the side stream only and the caller carries on there.
         compute = torch.cuda.current_stream(evidence.device)
         side = _side_stream(evidence.device)
-        side.wait_stream(compute)
+        wait_for_producer(side, compute, evidence)
         with torch.cuda.stream(side):
-            torch.distributed.all_reduce(evidence, op=torch.distributed.ReduceOp.SUM, group=group)
-            if average:
-                evidence.div_(world)
+            _reduce(evidence, group, average, world)
         evidence.record_stream(side)
         if join:
             compute.wait_stream(side)
+        return evidence
+    return _reduce(evidence, group, average, world)
+
+
+def wait_for_producer(side: torch.cuda.Stream, compute: torch.cuda.Stream, evidence: Tensor) -> None:
+    """Make `side` wait until `evidence` is complete.  The fused backward tags the evidence with
+    the event it records right after the evidence product (``_qste_ready``): waiting for that
+    instead of for the whole compute stream lets the side stream start while the dX product of
+    the same layer is still running."""
+
+    ready = getattr(evidence, "_qste_ready", None)
+    if ready is not None:
+        side.wait_event(ready)
+    else:
+        side.wait_stream(compute)
+
+
+def _reduce(evidence: Tensor, group, average: bool, world: int) -> Tensor:
+    """Sum over ranks, then the mean (src/qste/distributed.py:53-59 of the reference: all_reduce
+    then div_).  With NCCL and a power-of-two world the division rides the collective (ncclAvg
+    scales every rank's contribution by 1/world, which is exact for a power of two, so the
+    result is bit for bit the sum divided afterwards) and the separate pass over the 4 bytes per
+    coordinate disappears."""
+
+    if average and evidence.is_cuda and world & (world - 1) == 0 and \
+            torch.distributed.get_backend(group) == "nccl":
+        torch.distributed.all_reduce(evidence, op=torch.distributed.ReduceOp.AVG, group=group)
         return evidence
     torch.distributed.all_reduce(evidence, op=torch.distributed.ReduceOp.SUM, group=group)
     return evidence.div_(world) if average else evidence
 
 
-def mean_evidence(group=None, *, overlap: bool = False) -> Callable[[Tensor], Tensor]:
-    """Reducer that averages evidence over ranks (what DDP does to gradients)."""
+def _reserve_for_overlap(reserve_sms: int | None) -> None:
+    """An overlapped reducer's collective runs beside the persistent GEMMs of backward, which
+    otherwise hold every SM: keep a few out of their grids (8 unless told otherwise; the
+    environment variable QSTE_B200_RESERVED_SMS overrides the default)."""
+
+    import os
+
+    from . import kernels
+
+    if reserve_sms is None:
+        reserve_sms = int(os.environ.get("QSTE_B200_RESERVED_SMS", "8"))
+    kernels.set_backward_reserve(reserve_sms)
+
+
+def mean_evidence(group=None, *, overlap: bool = False, reserve_sms: int | None = None) -> Callable[[Tensor], Tensor]:
+    """Reducer that averages evidence over ranks (what DDP does to gradients).
+
+    ``overlap`` (not in the reference) runs the collective on a side stream beside the rest of
+    backward; ``reserve_sms`` is how many SMs the backward GEMMs then leave free for it."""
 
     def reduce(evidence: Tensor, *, join: bool = True) -> Tensor:
         if not _distributed_ready():
@@ -77,10 +119,12 @@ def mean_evidence(group=None, *, overlap: bool = False) -> Callable[[Tensor], Te
         return _all_reduce(evidence, group, average=True, overlap=overlap, join=join)
 
     reduce.side_stream = _side_stream if overlap else None
+    if overlap and _distributed_ready() and torch.distributed.get_world_size(group) > 1:
+        _reserve_for_overlap(reserve_sms)
     return reduce
 
 
-def sum_evidence(group=None, *, overlap: bool = False) -> Callable[[Tensor], Tensor]:
+def sum_evidence(group=None, *, overlap: bool = False, reserve_sms: int | None = None) -> Callable[[Tensor], Tensor]:
     """Reducer that sums evidence, for hosts that sum gradients."""
 
     def reduce(evidence: Tensor, *, join: bool = True) -> Tensor:
@@ -89,6 +133,8 @@ def sum_evidence(group=None, *, overlap: bool = False) -> Callable[[Tensor], Ten
         return _all_reduce(evidence, group, average=False, overlap=overlap, join=join)
 
     reduce.side_stream = _side_stream if overlap else None
+    if overlap and _distributed_ready() and torch.distributed.get_world_size(group) > 1:
+        _reserve_for_overlap(reserve_sms)
     return reduce
 
 

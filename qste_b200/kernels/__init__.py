@@ -89,8 +89,12 @@ def _workspace(device: torch.device, nbytes: int) -> Tensor:
            torch.cuda.current_stream(device).cuda_stream)
     held = _workspaces.get(key)
     if held is None or held.numel() < nbytes:
-        held = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[key] = held
+        grown = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        if held is not None:
+            # the first 256 bytes are the diagnostics header (wait counters, first give-up
+            # site, the work-item counter, which is zero between launches): it outlives the buffer
+            grown[:256].copy_(held[:256])
+        held = _workspaces[key] = grown
     return held
 
 
@@ -105,6 +109,25 @@ def wait_timeouts(device=None) -> int:
     if held is None:
         return 0
     return int(held[:8].view(torch.int64).item())
+
+
+def check_waits(device=None) -> None:
+    """Raise if a bounded device-side wait gave up in any call on `device` so far, on
+    whichever stream it ran: its output is then not to be trusted.  One 8-byte read per
+    workspace (one per stream that called a kernel); QSTEOptimizer.step() calls this where
+    it synchronises anyway."""
+
+    device = torch.device(device if device is not None else "cuda")
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    for (held_device, _), held in list(_workspaces.items()):
+        if held_device != index:
+            continue
+        if int(held[:8].view(torch.int64).item()):
+            word = int(held[200:208].view(torch.int64).item())
+            raise RuntimeError(
+                f"qste_b200: {int(held[:8].view(torch.int64).item())} bounded wait(s) inside a GEMM kernel gave up on "
+                f"cuda:{index} (first at csrc/gemm_tc.cu line {word >> 32}, block {(word >> 16) & 0xFFFF}, "
+                f"thread {word & 0xFFFF}); the results of that launch are incomplete.")
 
 
 def first_wait_timeout(device=None) -> dict | None:
@@ -390,16 +413,35 @@ def linear_backward_evidence(grad: Tensor, act_bits: Tensor, aux: Tensor, column
     return evidence, g_scale, g_bias
 
 
+_backward_reserve = 0
+
+
+def set_backward_reserve(count: int) -> int:
+    """How many SMs the GEMMs of :func:`linear_backward` leave free, for a collective that runs
+    beside backward on another stream (``distributed.mean_evidence(overlap=True)`` sets it).
+    Forward GEMMs never reserve any: no collective is in flight while they run.  Returns the
+    previous value."""
+
+    global _backward_reserve
+    previous, _backward_reserve = _backward_reserve, max(0, int(count))
+    return previous
+
+
 def linear_backward(grad: Tensor, weight_bits: Tensor, weight_scale: Tensor, columns: int,
-                    act_bits: Tensor, aux: Tensor, *, want_bias: bool = False):
+                    act_bits: Tensor, aux: Tensor, *, want_bias: bool = False, want_input: bool = True,
+                    evidence_ready: "torch.cuda.Event | None" = None):
     """The whole backward of a converted Linear in one library call.
 
     Returns ``(grad_input, evidence, grad_scale, grad_bias)``: ``grad_input`` in the dtype
     of ``grad`` (what ``packed_transpose`` returns), the rest as
     :func:`linear_backward_evidence` returns them.  One pass over ``grad`` yields the bias
     gradient, the offset correction and the gradient's largest magnitude, and both GEMMs
-    share one fp16 re-encoding of a bf16 gradient.  No counterpart in the reference's kernel
-    namespace (it is ``QSTELinearFn.backward``, functional.py:173-194, as one call).
+    share one fp16 re-encoding of a bf16 gradient.  The evidence product runs first:
+    ``evidence_ready``, when given, is recorded on the current stream once evidence, grad_scale
+    and grad_bias are complete and before the dX product is enqueued, so a reduction or an
+    update on another stream can wait for it and run beside dX.  ``want_input=False`` skips dX
+    (``grad_input`` is then ``None``).  No counterpart in the reference's kernel namespace (it is
+    ``QSTELinearFn.backward``, functional.py:173-194, as one call).
     """
 
     _need_cuda(grad, "linear_backward")
@@ -421,7 +463,7 @@ def linear_backward(grad: Tensor, weight_bits: Tensor, weight_scale: Tensor, col
     scale32 = _f32(weight_scale)
     act_bits = act_bits.contiguous()
     weight_bits = weight_bits.contiguous()
-    grad_input = torch.empty(samples, columns, dtype=grad.dtype, device=device)
+    grad_input = torch.empty(samples, columns, dtype=grad.dtype, device=device) if want_input else None
     evidence = torch.empty(rows, columns, dtype=torch.float32, device=device)
     g_scale = torch.empty(rows, dtype=torch.float32, device=device)
     g_bias = torch.empty(rows, dtype=torch.float32, device=device) if want_bias else None
@@ -430,16 +472,30 @@ def linear_backward(grad: Tensor, weight_bits: Tensor, weight_scale: Tensor, col
         g_scale.zero_()
         if g_bias is not None:
             g_bias.zero_()
+        if evidence_ready is not None:
+            evidence_ready.record()
         return grad_input, evidence, g_scale, g_bias
     code = _DTYPES[grad.dtype]
     library = _cabi.load()
+    event = None
+    if evidence_ready is not None:
+        if not evidence_ready.cuda_event:
+            evidence_ready.record()  # torch creates the CUDA event at its first record
+        event = ctypes.c_void_p(evidence_ready.cuda_event)
     with torch.cuda.device(device):
-        need = library.qste_b200_linear_backward_workspace(samples, rows, columns, code)
-        workspace = _workspace(device, need)
-        _cabi.check(library.qste_b200_linear_backward(
-            _ptr(grad), code, samples, rows, _ptr(weight_bits), _ptr(scale32), columns, _ptr(act_bits),
-            _ptr(aux32), _ptr(grad_input), code, _ptr(evidence), _ptr(g_scale), _ptr(g_bias),
-            _ptr(workspace), workspace.numel(), _stream(device)), "linear_backward")
+        reserve = _backward_reserve
+        if reserve:
+            library.qste_b200_set_reserved_sms(reserve)
+        try:
+            need = library.qste_b200_linear_backward_workspace(samples, rows, columns, code)
+            workspace = _workspace(device, need)
+            _cabi.check(library.qste_b200_linear_backward_staged(
+                _ptr(grad), code, samples, rows, _ptr(weight_bits), _ptr(scale32), columns, _ptr(act_bits),
+                _ptr(aux32), _ptr(grad_input), code, _ptr(evidence), _ptr(g_scale), _ptr(g_bias), event,
+                _ptr(workspace), workspace.numel(), _stream(device)), "linear_backward")
+        finally:
+            if reserve:
+                library.qste_b200_set_reserved_sms(0)
     return grad_input, evidence, g_scale, g_bias
 
 
@@ -489,21 +545,14 @@ def packed_embedding(ids: Tensor, packed: Tensor, scale: Tensor, columns: int) -
 
 # -- optimizer --------------------------------------------------------------------
 
-def coordinate_update(gradient: Tensor, coordinate: Tensor, packed: Tensor, moment_q: Tensor,
-                      moment_scale: Tensor, row_v: Tensor, col_v: Tensor, *, beta1: float,
-                      beta2: float, update_clip: float, coordinate_lr: float, block_size: int,
-                      seed: int, step, flips: Tensor | None = None,
-                      update_enabled: Tensor | None = None):
-    """One fused coordinate step, in place (loader.py:329-368).
+def _check_update_arguments(what, gradient, coordinate, packed, moment_q, moment_scale, row_v, col_v,
+                            block_size, step, flips, update_enabled) -> int:
+    """Everything either coordinate-update wrapper must know before a pointer is taken:
+    devices, dtypes, shapes and contiguity of the in-place state (the conditions of the
+    reference's TORCH_CHECKs, cpu.cpp:584-606, and cuda.py:1731-1732 for the block size).
+    Shapes and dtypes are checked before devices, so a malformed call is refused the same way
+    wherever its tensors live.  Returns the number of coordinates."""
 
-    ``gradient`` is consumed as scratch.  With ``flips=None`` the flip count is
-    returned as an ``int`` (one host synchronisation); pass a device int64 tensor to
-    get it there instead, and device tensors for ``step`` (int64) and
-    ``update_enabled`` (uint8) to keep the whole call free of host reads, which is
-    what CUDA-graph capture needs (cuda.py:1705-1812 of the reference).
-    """
-
-    _need_cuda(gradient, "coordinate_update")
     block_size = int(block_size)
     if block_size <= 0 or block_size & (block_size - 1):
         raise ValueError("momentum block size must be a positive power of two")
@@ -528,17 +577,41 @@ def coordinate_update(gradient: Tensor, coordinate: Tensor, packed: Tensor, mome
                          ("moment_scale", moment_scale), ("row_v", row_v), ("col_v", col_v)):
         if not tensor.is_contiguous():
             raise RuntimeError(f"{name} must be contiguous: it is updated in place")
+        if tensor.device != gradient.device:
+            raise RuntimeError(f"{name} is on {tensor.device}, the evidence on {gradient.device}")
+    if torch.is_tensor(step) and (step.dtype != torch.int64 or step.device != gradient.device):
+        raise RuntimeError("a tensor step must be an int64 scalar on the evidence's device")
+    if update_enabled is not None and (update_enabled.dtype != torch.uint8 or update_enabled.device != gradient.device):
+        raise RuntimeError("update_enabled must be a uint8 scalar tensor on the evidence's device")
+    if flips is not None and (flips.dtype != torch.int64 or flips.numel() != 1 or flips.device != gradient.device):
+        raise RuntimeError("flips must be an int64 scalar tensor on the evidence's device")
+    _need_cuda(gradient, what)
+    return count
+
+
+def coordinate_update(gradient: Tensor, coordinate: Tensor, packed: Tensor, moment_q: Tensor,
+                      moment_scale: Tensor, row_v: Tensor, col_v: Tensor, *, beta1: float,
+                      beta2: float, update_clip: float, coordinate_lr: float, block_size: int,
+                      seed: int, step, flips: Tensor | None = None,
+                      update_enabled: Tensor | None = None):
+    """One fused coordinate step, in place (loader.py:329-368).
+
+    ``gradient`` is consumed as scratch.  With ``flips=None`` the flip count is
+    returned as an ``int`` (one host synchronisation); pass a device int64 tensor to
+    get it there instead, and device tensors for ``step`` (int64) and
+    ``update_enabled`` (uint8) to keep the whole call free of host reads, which is
+    what CUDA-graph capture needs (cuda.py:1705-1812 of the reference).
+    """
+
+    count = _check_update_arguments("coordinate_update", gradient, coordinate, packed, moment_q, moment_scale,
+                                    row_v, col_v, block_size, step, flips, update_enabled)
+    block_size = int(block_size)
+    rows, columns = gradient.shape
     if count == 0:
         return 0 if flips is None else flips.zero_()
     device = gradient.device
     gradient = gradient if gradient.is_contiguous() else gradient.contiguous()
     step_tensor = step if torch.is_tensor(step) else None
-    if step_tensor is not None and (step_tensor.dtype != torch.int64 or step_tensor.device != device):
-        raise RuntimeError("a tensor step must be an int64 scalar on the evidence's device")
-    if update_enabled is not None and update_enabled.dtype != torch.uint8:
-        raise RuntimeError("update_enabled must be a uint8 scalar tensor")
-    if flips is not None and flips.dtype != torch.int64:
-        raise RuntimeError("flips must be an int64 scalar tensor")
     library = _cabi.load()
     with torch.cuda.device(device):
         need = library.qste_b200_coordinate_update_workspace(rows, columns, block_size)
@@ -569,7 +642,16 @@ def coordinate_update_static(gradient: Tensor, coordinate: Tensor, packed: Tenso
     race.  ``flips`` (a device int64 scalar) is required and receives the flip count.
     """
 
-    _need_cuda(gradient, "coordinate_update_static")
+    if not torch.is_tensor(flips):
+        raise RuntimeError("coordinate_update_static needs `flips`, a device int64 scalar: there is no workspace "
+                           "to read the count back from")
+    if not gradient.is_contiguous():
+        # the workspace variant copies a strided evidence; this one may not allocate the copy
+        raise RuntimeError("coordinate_update_static: the evidence must be contiguous (no copy can be allocated here)")
+    count = _check_update_arguments("coordinate_update_static", gradient, coordinate, packed, moment_q,
+                                    moment_scale, row_v, col_v, block_size, int(step), flips, None)
+    if count == 0:
+        return flips.zero_()
     rows, columns = gradient.shape
     device = gradient.device
     with torch.cuda.device(device):
@@ -621,6 +703,6 @@ __all__ = [
     "DeviceProfile", "apply_bits", "coordinate_update", "coordinate_update_static", "cuda_available", "cuda_backend",
     "evidence_from_packed", "linear_backward", "linear_backward_evidence", "native_available", "pack_bits",
     "pack_coordinate", "pack_affine_rows", "packed_embedding", "packed_linear_affine",
-    "packed_row_inner", "packed_transpose", "profile", "status", "stream", "unpack_bits",
-    "unpack_rows", "wait_timeouts", "warm", "warn_if_slow", "first_wait_timeout",
+    "packed_row_inner", "packed_transpose", "profile", "set_backward_reserve", "status", "stream", "unpack_bits",
+    "unpack_rows", "wait_timeouts", "warm", "warn_if_slow", "first_wait_timeout", "check_waits",
 ]

@@ -18,6 +18,7 @@ SYMBOLS = (
     "qste_b200_status_string",
     "qste_b200_last_cuda_error",
     "qste_b200_launch_count",
+    "qste_b200_set_reserved_sms",
     "qste_b200_pack_coordinate",
     "qste_b200_pack_affine_rows",
     "qste_b200_pack_bits",
@@ -33,6 +34,7 @@ SYMBOLS = (
     "qste_b200_linear_backward_evidence",
     "qste_b200_linear_backward_workspace",
     "qste_b200_linear_backward",
+    "qste_b200_linear_backward_staged",
     "qste_b200_packed_row_inner",
     "qste_b200_packed_embedding",
     "qste_b200_coordinate_update_workspace",
@@ -53,6 +55,7 @@ _SIGNATURES = {
     "qste_b200_status_string": (ctypes.c_char_p, [_int]),
     "qste_b200_last_cuda_error": (ctypes.c_char_p, []),
     "qste_b200_launch_count": (ctypes.c_ulonglong, []),
+    "qste_b200_set_reserved_sms": (_int, [_int]),
     "qste_b200_pack_coordinate": (_int, [_p, _i64, _i64, _p, _p]),
     "qste_b200_pack_affine_rows": (_int, [_p, _int, _i64, _i64, _p, _p, _p, _p]),
     "qste_b200_pack_bits": (_int, [_p, _i64, _i64, _p, _p]),
@@ -73,6 +76,8 @@ _SIGNATURES = {
     "qste_b200_linear_backward_workspace": (_size, [_i64, _i64, _i64, _int]),
     "qste_b200_linear_backward": (
         _int, [_p, _int, _i64, _i64, _p, _p, _i64, _p, _p, _p, _int, _p, _p, _p, _p, _size, _p]),
+    "qste_b200_linear_backward_staged": (
+        _int, [_p, _int, _i64, _i64, _p, _p, _i64, _p, _p, _p, _int, _p, _p, _p, _p, _p, _size, _p]),
     "qste_b200_packed_row_inner": (_int, [_p, _p, _i64, _i64, _p, _p]),
     "qste_b200_packed_embedding": (_int, [_p, _i64, _p, _p, _i64, _i64, _p, _int, _p, _p]),
     "qste_b200_coordinate_update_workspace": (_size, [_i64, _i64, _i64]),

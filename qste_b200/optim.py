@@ -97,6 +97,10 @@ class QSTEOptimizer:
                 "col_v": torch.zeros(surface.columns, dtype=torch.float16, device=device),
             }
             surface._immediate = self._apply
+            if device.type == "cuda" and device not in self._device_flips:
+                # made here, on the stream the model was built on, so that its zero fill is
+                # long done before any side stream first adds to it
+                self._device_flips[device] = torch.zeros((), dtype=torch.int64, device=device)
         for surface in self.surfaces:
             kernels.warm(surface.coordinate.device)
             kernels.warn_if_slow(surface.coordinate.device.type)
@@ -167,10 +171,10 @@ class QSTEOptimizer:
             # No reduction to wait for: the update still goes to the side stream, where its small
             # memory-bound kernels fill in beside the next layer's backward (3 % of the step on
             # one GPU).  Same kernels, same inputs: the result does not depend on the stream.
-            from .distributed import _side_stream
+            from .distributed import _side_stream, wait_for_producer
 
             side = _side_stream(evidence.device)
-            side.wait_stream(torch.cuda.current_stream(evidence.device))
+            wait_for_producer(side, torch.cuda.current_stream(evidence.device), evidence)
             evidence.record_stream(side)
             self._side_streams.add(side)
         arguments = dict(
@@ -186,7 +190,10 @@ class QSTEOptimizer:
             device = evidence.device
             total = self._device_flips.get(device)
             if total is None:
-                total = self._device_flips[device] = torch.zeros((), dtype=torch.int64, device=device)
+                # a surface moved to another device after construction: make the counter where the
+                # zero fill is ordered before the add below, whichever stream that runs on
+                with torch.cuda.stream(side) if side is not None else contextlib.nullcontext():
+                    total = self._device_flips[device] = torch.zeros((), dtype=torch.int64, device=device)
             with torch.cuda.stream(side) if side is not None else contextlib.nullcontext():
                 scratch = torch.empty((), dtype=torch.int64, device=device)
                 kernels.coordinate_update(*tensors, flips=scratch, **arguments)
@@ -212,9 +219,12 @@ class QSTEOptimizer:
             torch.cuda.current_stream(side.device).wait_stream(side)
         self._side_streams.clear()
         flips = self._flips
-        for counter in self._device_flips.values():
+        for device, counter in self._device_flips.items():
             flips += int(counter.item())
             counter.zero_()
+            # the read above synchronised with everything this step launched on the device: if a
+            # GEMM's bounded wait gave up anywhere in it, say so instead of training on
+            kernels.check_waits(device)
         self._flips = 0
         self.step_number += 1
         return flips

@@ -79,8 +79,10 @@ def linear_backward_evidence(grad, act_bits, aux, columns, weight_bits, weight_s
     return _t(evidence), _t(g_scale), g_bias
 
 
-def linear_backward(grad, weight_bits, weight_scale, columns, act_bits, aux, *, want_bias=False):
-    grad_input = packed_transpose(grad, weight_bits, columns, row_scale=weight_scale)
+def linear_backward(grad, weight_bits, weight_scale, columns, act_bits, aux, *, want_bias=False, want_input=True,
+                    evidence_ready=None):
+    del evidence_ready  # a CUDA event; CPU tensors never carry one
+    grad_input = packed_transpose(grad, weight_bits, columns, row_scale=weight_scale) if want_input else None
     evidence, g_scale, g_bias = linear_backward_evidence(grad, act_bits, aux, columns, weight_bits,
                                                          weight_scale, want_bias=want_bias)
     return grad_input, evidence, g_scale, g_bias

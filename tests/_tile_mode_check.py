@@ -1,15 +1,18 @@
 """Run by test_gpu_kernels.py in a child process, because the GEMM's tile mode is chosen from
-environment variables that the library reads once: checks the three packed-sign GEMMs against
-the CUDA-core kernel on shapes large enough for 256-row tiles, and prints OK."""
+environment variables that the library reads once: checks the three packed-sign GEMMs on shapes large
+enough for 256-row tiles against the CPU oracle (128 sampled rows of every output) and, over the
+whole output, against the CUDA-core kernel (itself oracle-checked elsewhere), and prints OK."""
 
 import os
 import sys
 from contextlib import contextmanager
 from pathlib import Path
 
+import numpy as np
 import torch
 
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+import oracle  # noqa: E402
 from qste_b200 import kernels  # noqa: E402
 
 
@@ -28,6 +31,33 @@ def forced_path(name):
 
 def rel(a, b):
     return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+
+
+def against_oracle(got, want, what):
+    want = torch.from_numpy(np.ascontiguousarray(want))
+    if got.dtype != torch.float32:
+        want = want.to(got.dtype)  # like for like: the oracle's fp32 result rounded as the kernel rounds
+    error = rel(got.cpu(), want)
+    assert error <= 1e-3, (what, error)
+
+
+def oracle_checks(x, dy, bits, scale, bias, columns, y, dx, fused, saved, generator):
+    """128 sampled rows of Y, dX, the evidence and the scale gradient against the oracle."""
+
+    samples, rows = dy.shape
+    act_bits, act_offset, act_scale = (t.cpu().numpy() for t in saved)
+    tokens = torch.randperm(samples, generator=generator)[:128]
+    outputs = torch.randperm(rows, generator=generator)[:128]
+    xs, dys, bits_host, scale_host = x.cpu()[tokens].float(), dy.cpu().float(), bits.cpu(), scale.cpu()
+    against_oracle(y[tokens.to(y.device)], oracle.packed_linear_affine(xs, bits_host, scale_host, bias.cpu(), columns), "forward")
+    if dx is not None:
+        against_oracle(dx[tokens.to(y.device)], oracle.packed_transpose(dys[tokens], bits_host, columns, scale_host), "dX")
+    grad = dys[:, outputs].contiguous()
+    plain = oracle.evidence_from_packed(grad, act_bits, columns, act_scale)
+    decoded = plain.astype(np.float64) + (grad.double().t().numpy() @ act_offset.astype(np.float64))[:, None]
+    against_oracle(fused[0][outputs.to(y.device)], (decoded * scale_host[outputs].double().numpy()[:, None]).astype(np.float32), "evidence")
+    against_oracle(fused[1][outputs.to(y.device)],
+                   oracle.packed_row_inner(decoded.astype(np.float32), bits_host[outputs].contiguous(), columns), "scale gradient")
 
 
 def stress_short_items(device, generator):
@@ -80,6 +110,8 @@ def main():
         if rows % 64 == 0:
             dx = kernels.packed_transpose(dy, bits, columns, scale)
         fused = kernels.linear_backward_evidence(dy, act_bits, aux, columns, bits, scale, want_bias=True)
+        oracle_checks(x, dy, bits, scale, bias, columns, y, dx if rows % 64 == 0 else None, fused,
+                      (act_bits, act_offset, act_scale), generator)
         with forced_path("simt"):
             y_ref = kernels.packed_linear_affine(x.float(), bits, scale, bias, columns)
             assert rel(y, y_ref) <= 4e-3, ("forward", rel(y, y_ref))  # bf16 output rounding

@@ -1,7 +1,8 @@
 """Generate tests/golden/reference_vectors.npz by running the reference itself.
 
-Run where the reference is checked out; its location is the first argument (the default is
-the constant REFERENCE below):
+Run where the reference is checked out; its location is the first argument, else the
+environment variable QSTE_REFERENCE, else a directory named ``reference`` beside this
+repository:
 
     QSTE_NATIVE_ARCH=0 QSTE_CACHE_DIR=/tmp/qste_cache python tests/golden/make_golden.py [reference]
 
@@ -23,7 +24,8 @@ os.environ.setdefault("QSTE_NATIVE_ARCH", "0")
 os.environ.setdefault("QSTE_CACHE_DIR", "/tmp/qste_cache_golden")
 os.environ.setdefault("QSTE_KERNELS", "native")
 
-REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+REFERENCE = Path(sys.argv[1] if len(sys.argv) > 1 else
+                 os.environ.get("QSTE_REFERENCE") or Path(__file__).resolve().parents[3] / "reference")
 sys.path.insert(0, str(REFERENCE / "src"))
 
 import numpy as np  # noqa: E402

@@ -166,3 +166,54 @@ def test_evidence_full_size_properties():
     assert rel(g_bias, dy.float().sum(0)) <= 1e-5
     assert rel(dx, kernels.packed_transpose(dy, bits, DIM, scale)) <= 2e-3
     assert kernels.wait_timeouts() == 0
+
+
+# ---------------------------------------------------------------------------------------
+# the CUDA kernels against the reference's own compiled CPU kernels (no restatement between)
+# ---------------------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def compiled_reference():
+    from oracle import build_ref
+
+    module = build_ref.load()
+    if module is None:
+        pytest.skip("oracle/_ref/qste_cpu.so was not built (no reference checkout where this tree was built)")
+    return module
+
+
+def test_pack_affine_rows_full_size_equals_the_compiled_reference(compiled_reference):
+    x = torch.randn(TOKENS, DIM, generator=torch.Generator().manual_seed(23)).to(torch.bfloat16)
+    want = compiled_reference.pack_affine_rows(x.float())
+    got = kernels.pack_affine_rows(x.to(DEVICE))
+    for mine, theirs in zip(got, want):
+        assert torch.equal(mine.cpu(), theirs)
+
+
+@pytest.mark.parametrize("rows,columns,steps", [(2048, 2048, 3), (FFN, DIM, 1)])
+def test_coordinate_update_equals_the_compiled_reference(compiled_reference, rows, columns, steps):
+    """cpu.cpp:578-808 itself, compiled: the single-layer configuration over three steps and
+    one step of the 58.7 M-coordinate surface."""
+
+    generator = torch.Generator().manual_seed(37)
+    coordinate = torch.randint(-127, 128, (rows, columns), generator=generator, dtype=torch.int32).to(torch.int8)
+    cpu = {
+        "coordinate": coordinate,
+        "packed": compiled_reference.pack_coordinate(coordinate),
+        "moment_q": torch.zeros(rows, columns, dtype=torch.int8),
+        "moment_scale": torch.full((rows * columns // 256,), 1 / 127, dtype=torch.float16),
+        "row_v": torch.zeros(rows, dtype=torch.float16),
+        "col_v": torch.zeros(columns, dtype=torch.float16),
+    }
+    gpu = {k: v.clone().to(DEVICE) for k, v in cpu.items()}
+    for step in range(steps):
+        evidence = torch.randn(rows, columns, generator=generator) * (3.0 if step == 0 else 0.1)
+        want = compiled_reference.coordinate_update(evidence.clone(), *[cpu[k] for k in ORDER], 0.9, 0.99, 2.0, 1.0, 256, 5, step)
+        got = kernels.coordinate_update(evidence.to(DEVICE), *[gpu[k] for k in ORDER], beta1=0.9, beta2=0.99,
+                                        update_clip=2.0, coordinate_lr=1.0, block_size=256, seed=5, step=step)
+        assert got == int(want)
+        for key in ORDER:
+            mine, theirs = gpu[key].cpu(), cpu[key]
+            if mine.dtype == torch.float16:
+                mine, theirs = mine.view(torch.int16), theirs.view(torch.int16)
+            assert torch.equal(mine, theirs), (key, step, int((mine != theirs).sum()))

@@ -239,6 +239,11 @@ def test_tensor_core_transpose(samples, rows, columns, dtype):
         cross = kernels.packed_transpose(dy.to(DEVICE).float(), bits.to(DEVICE), columns, scale.to(DEVICE))
     # the row scale rides the tensor-core operand in fp16 (2^-12 relative per term)
     assert rel(host(dx), like(host(cross), dtype)) <= 1e-3
+    # and against the oracle itself: whole output when that takes seconds, else 128 sampled rows
+    picked = torch.arange(samples) if samples * rows * columns <= 1 << 28 else \
+        torch.randperm(samples, generator=torch.Generator().manual_seed(1))[:128]
+    want = oracle.packed_transpose(dy[picked].float(), bits, columns, scale)
+    assert rel(host(dx[picked.to(DEVICE)]), like(want, dtype)) <= 1e-3
     assert kernels.wait_timeouts() == 0
 
 
@@ -260,6 +265,17 @@ def test_tensor_core_evidence(samples, rows, columns, dtype):
     with forced_path("simt"):
         plain_cross = kernels.evidence_from_packed(dy.to(DEVICE).float(), act_bits, columns, act_scale)
     assert rel(host(plain), host(plain_cross)) <= 1e-3
+    # and against the oracle itself: every row when that takes seconds, else 128 sampled rows
+    picked = torch.arange(rows) if samples * rows * columns <= 1 << 28 else \
+        torch.randperm(rows, generator=torch.Generator().manual_seed(2))[:128]
+    grad = dy[:, picked].float().contiguous()
+    want_plain = oracle.evidence_from_packed(grad, host(act_bits), columns, host(act_scale))
+    assert rel(host(plain[picked.to(DEVICE)]), want_plain) <= 1e-3
+    decoded = want_plain.astype(np.float64) + (grad.double().t().numpy() @ host(act_offset).astype(np.float64))[:, None]
+    assert rel(host(fused[0][picked.to(DEVICE)]), decoded * scale[picked].double().numpy()[:, None]) <= 1e-3
+    assert rel(host(fused[1][picked.to(DEVICE)]),
+               oracle.packed_row_inner(decoded.astype(np.float32), bits[picked].contiguous(), columns)) <= 1e-3
+    assert rel(host(fused[2]), dy.double().sum(0).numpy()) <= 1e-5
     assert kernels.wait_timeouts() == 0
 
 

@@ -38,6 +38,14 @@ def test_golden_training_steps_on_the_gpu(golden, case, use_bias):
     assert np.array_equal(layer.surface.packed_sign.cpu().numpy(), golden(case, "init_packed"))
     coordinates = qste.QSTEOptimizer(model)
     host = torch.optim.AdamW(qste.continuous_parameters(model), lr=1e-3)
+    # the evidence each step hands the optimizer, so the oracle can be walked beside the GPU
+    captured = []
+    apply = coordinates._apply
+    layer.surface._immediate = lambda s, e: (captured.append(e.detach().cpu().numpy().copy()), apply(s, e))
+    shadow = {key: golden(case, f"init_{key}").copy() for key in ("coordinate", "packed")}
+    blocks = (rows * columns + 255) // 256
+    shadow.update(moment_q=np.zeros((rows, columns), np.int8), moment_scale=np.full(blocks, 1 / 127, np.float16),
+                  row_v=np.zeros(rows, np.float16), col_v=np.zeros(columns, np.float16))
     for number in range(2):
         x = torch.from_numpy(golden(case, f"x{number}")).to(DEVICE).requires_grad_(True)
         y = model(x)
@@ -55,11 +63,49 @@ def test_golden_training_steps_on_the_gpu(golden, case, use_bias):
         state = coordinates.state[id(layer.surface)]
         # the evidence GEMM sums in another order than MKL did, so a coordinate whose
         # rounding draw sits within an ulp of its threshold may land on the other side
-        difference = np.abs(layer.surface.coordinate.cpu().numpy().astype(np.int32)
-                            - golden(case, f"coordinate{number}").astype(np.int32))
+        mine = layer.surface.coordinate.cpu().numpy()
+        difference = np.abs(mine.astype(np.int32) - golden(case, f"coordinate{number}").astype(np.int32))
         assert difference.max() <= 1 and (difference > 0).mean() < 0.002
         assert abs(flips - int(np.ravel(golden(case, f"flips{number}"))[0])) <= 4
         assert (state["moment_q"].cpu().numpy() != golden(case, f"moment_q{number}")).mean() < 0.01
+
+        # Given the SAME evidence the oracle lands on the GPU's state byte for byte ...
+        want_flips = oracle.coordinate_update(
+            captured[number].copy(), shadow["coordinate"], shadow["packed"], shadow["moment_q"], shadow["moment_scale"],
+            shadow["row_v"], shadow["col_v"], beta1=0.9, beta2=0.99, update_clip=2.0, coordinate_lr=1.0,
+            block_size=256, seed=1, step=number)
+        assert np.array_equal(mine, shadow["coordinate"]) and flips == want_flips
+        assert np.array_equal(state["moment_q"].cpu().numpy(), shadow["moment_q"])
+        # ... and where the result differs from the reference's own run, the coordinate is a
+        # near-tie of the stochastic rounding.  Start the oracle from the REFERENCE's state before
+        # this step and give it the GPU's evidence (which depends on the step's inputs, not on the
+        # coordinates): every coordinate that then differs from the reference's has its uniform
+        # draw within a hair of the fractional part of its target (cpu.cpp:762-772), so the last
+        # bits of the evidence sum -- the order MKL happened to add in -- decide it.
+        def reference_state(name):
+            if number > 0:
+                array = golden(case, f"{name}{number - 1}").copy()
+                return array.view(np.float16) if array.dtype == np.uint16 else array
+            if name in ("coordinate", "packed"):
+                return golden(case, f"init_{name}").copy()
+            return {"moment_q": np.zeros((rows, columns), np.int8), "moment_scale": np.full(blocks, 1 / 127, np.float16),
+                    "row_v": np.zeros(rows, np.float16), "col_v": np.zeros(columns, np.float16)}[name]
+
+        start = {key: reference_state(key) for key in ("coordinate", "packed", "moment_q", "moment_scale", "row_v", "col_v")}
+        before = start["coordinate"].astype(np.float32)
+        moment = captured[number].copy()
+        _, taps = oracle.coordinate_update(
+            moment, start["coordinate"], start["packed"], start["moment_q"], start["moment_scale"], start["row_v"],
+            start["col_v"], beta1=0.9, beta2=0.99, update_clip=2.0, coordinate_lr=1.0, block_size=256, seed=1,
+            step=number, taps=True)
+        apart = np.abs(start["coordinate"].astype(np.int32) - golden(case, f"coordinate{number}").astype(np.int32))
+        assert apart.max() <= 1
+        target = before - moment * np.float32(taps["coordinate_step"])
+        fraction = target - np.floor(target)
+        for row, column in zip(*np.nonzero(apart)):
+            draw = oracle.uniform(1, number, int(row) * columns + int(column))
+            f = float(fraction[row, column])
+            assert min(abs(draw - f), f, 1.0 - f) < 1e-4, (number, int(row), int(column), draw, f)
 
 
 def test_config_one_layer_matches_the_oracle():

@@ -347,3 +347,50 @@ def test_product_kernels_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         kernels.packed_linear_affine(torch.zeros(2, 8), torch.zeros(4, 1, dtype=torch.uint8),
                                      torch.ones(4), None, 8)
+
+
+def _update_arguments(rows=6, columns=16, block=64):
+    blocks = (rows * columns + block - 1) // block
+    return dict(gradient=torch.zeros(rows, columns), coordinate=torch.zeros(rows, columns, dtype=torch.int8),
+                packed=torch.zeros(rows, (columns + 7) // 8, dtype=torch.uint8),
+                moment_q=torch.zeros(rows, columns, dtype=torch.int8),
+                moment_scale=torch.zeros(blocks, dtype=torch.float16), row_v=torch.zeros(rows, dtype=torch.float16),
+                col_v=torch.zeros(columns, dtype=torch.float16))
+
+
+@pytest.mark.parametrize("entry", ["coordinate_update", "coordinate_update_static"])
+@pytest.mark.parametrize("change,error,match", [
+    (dict(gradient=torch.zeros(6, 16, dtype=torch.float64)), RuntimeError, "float32"),
+    (dict(coordinate=torch.zeros(6, 16, dtype=torch.int16)), RuntimeError, "dtypes"),
+    (dict(moment_q=torch.zeros(6, 8, dtype=torch.int8)), RuntimeError, "coordinate state shape"),
+    (dict(packed=torch.zeros(6, 1, dtype=torch.uint8)), RuntimeError, "packed sign shape"),
+    (dict(moment_scale=torch.zeros(1, dtype=torch.float16)), RuntimeError, "momentum scale shape"),
+    (dict(moment_scale=torch.zeros(2, dtype=torch.float32)), RuntimeError, "float16"),
+    (dict(row_v=torch.zeros(5, dtype=torch.float16)), RuntimeError, "factored statistics"),
+    (dict(col_v=torch.zeros(17, dtype=torch.float16)), RuntimeError, "factored statistics"),
+    (dict(coordinate=torch.zeros(16, 6, dtype=torch.int8).t()), RuntimeError, "contiguous"),
+    (dict(block_size=48), ValueError, "power of two"),
+    (dict(flips=torch.zeros((), dtype=torch.int32)), RuntimeError, "flips must be an int64"),
+    (dict(flips=torch.zeros(2, dtype=torch.int64)), RuntimeError, "flips must be an int64"),
+])
+def test_both_update_wrappers_refuse_malformed_state_before_the_library_is_called(entry, change, error, match):
+    """Short, strided or wrongly typed state must never reach a kernel as a raw pointer: both
+    wrappers run the same checks (those of cpu.cpp:584-606 of the reference) first."""
+
+    arguments = _update_arguments()
+    options = dict(beta1=0.9, beta2=0.99, update_clip=2.0, coordinate_lr=1.0, block_size=64, seed=1, step=0,
+                   flips=torch.zeros((), dtype=torch.int64))
+    for key, value in change.items():
+        (options if key in options else arguments)[key] = value
+    with pytest.raises(error, match=match):
+        getattr(kernels, entry)(*arguments.values(), **options)
+
+
+def test_the_allocation_free_update_refuses_what_it_cannot_copy():
+    arguments = _update_arguments()
+    options = dict(beta1=0.9, beta2=0.99, update_clip=2.0, coordinate_lr=1.0, block_size=64, seed=1, step=0)
+    with pytest.raises(RuntimeError, match="needs `flips`"):
+        kernels.coordinate_update_static(*arguments.values(), flips=None, **options)
+    arguments["gradient"] = torch.zeros(16, 6).t()
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        kernels.coordinate_update_static(*arguments.values(), flips=torch.zeros((), dtype=torch.int64), **options)
