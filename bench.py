@@ -29,6 +29,7 @@ import statistics
 import sys
 import threading
 import time
+from contextlib import nullcontext
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
@@ -331,13 +332,13 @@ def _gemm_inputs(device, m, k, n, seed=2):
     return x, bits, scale
 
 
-def kernel_roofline(device, tokens: int) -> dict:
+def kernel_roofline(device, tokens: int, dim: int = D_MODEL, ffn: int = D_FFN) -> dict:
     """The dominant kernel alone: forward packed-sign GEMM of the up projection,
-    [tokens, 4096] x [14336, 4096]^T, bf16 in, fp32 accumulate, bf16 out."""
+    [tokens, dim] x [ffn, dim]^T (4096 -> 14336 by default), bf16 in, fp32 accumulate, bf16 out."""
 
     from qste_b200 import kernels
 
-    m, k, n = tokens, D_MODEL, D_FFN
+    m, k, n = tokens, dim, ffn
     x, bits, scale = _gemm_inputs(device, m, k, n)
     for _ in range(3):
         kernels.packed_linear_affine(x, bits, scale, None, k)
@@ -349,13 +350,13 @@ def kernel_roofline(device, tokens: int) -> dict:
     return {"bound": "tensor", "kernel": "packed-sign forward GEMM", "shape": [m, k, n],
             "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
             "frac": achieved / peak["bf16_tflops"], "peak_source": peak["source"],
-            # dram__bytes_read.sum + dram__bytes_write.sum of this kernel in the ncu capture summarised
-            # in profiles/packed_gemm_tc_forward_2048x4096x14336.md (50.4 MB per launch at 2048
-            # tokens: 24.4 read + 26.0 written, part of the output still in L2 when the capture
-            # ended), scaled to this launch by the token count: activations in and out grow with
-            # it, the 7.3 MB of bits, read once, do not
-            "traffic": (50.4e6 - 7.3e6) * m / 2048 + 7.3e6,
-            "traffic_source": "ncu capture at 2048 tokens, scaled by the token count",
+            # dram__bytes_read.sum + dram__bytes_write.sum of this kernel, one launch captured at the
+            # bench's own 16384 tokens (profiles/packed_gemm_tc_three_products_16384x4096x14336.md:
+            # 151.4 MB read + 449.7 MB written; algorithmic 611 MB, the last tiles of Y were still in
+            # L2).  Other token counts: activations in and out scale with the tokens, the bits do not.
+            "traffic": ((601.1e6 - 7.3e6) * m / 16384 + 7.3e6) if (k, n) == (D_MODEL, D_FFN) else None,
+            "traffic_source": "ncu capture of one launch at 16384 tokens" + ("" if m == 16384 else ", scaled by the token count"),
+            "algorithmic_bytes": m * k * 2 + n * k / 8 + 4 * n + m * n * 2,
             "us_per_launch": seconds * 1e6}
 
 
@@ -454,6 +455,309 @@ def kernel_breakdown(device, tokens: int) -> dict:
     stream("forward_m1_stream", lambda: kernels.packed_linear_affine(x1, bits1, scale1, None, k),
            n * k / 8 + 4 * n + 2 * k + 2 * n, repeat=20, replay=True)
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# decoder workloads: the GPT-2-small and Llama-1.1B shapes with their MLPs converted
+# (harness models in plain PyTorch: the reference ships none, only the training loop they plug into)
+# ------------------------------------------------------------------------------------------
+
+DECODERS = {
+    # configs[2]: 12 layers, d = 768, 12 heads, MLP ratio 4, GELU, vocab 50257, seq 1024, batch 8, one GPU
+    "gpt2_small": dict(layers=12, dim=768, heads=12, kv_heads=12, ffn=3072, mlp="gelu", norm="layer", rope=False,
+                       vocab=50257, seq=1024, global_batch=8, micro_batch=8, tied_head=True,
+                       include=["blocks.*.mlp.fc", "blocks.*.mlp.proj"]),
+    # configs[3]: 22 layers, d = 2048, ffn 5632, 32 heads / 4 KV heads, RoPE, RMSNorm, vocab 32000, seq 2048,
+    # global batch 64 sequences over the GPUs of the job (strong scaling)
+    "llama_1b": dict(layers=22, dim=2048, heads=32, kv_heads=4, ffn=5632, mlp="swiglu", norm="rms", rope=True,
+                     vocab=32000, seq=2048, global_batch=64, micro_batch=8, tied_head=False,
+                     include=["blocks.*.mlp.gate", "blocks.*.mlp.up", "blocks.*.mlp.down"]),
+}
+
+
+class DecoderMLP(nn.Module):
+    def __init__(self, spec, device):
+        super().__init__()
+        dim, ffn = spec["dim"], spec["ffn"]
+        if spec["mlp"] == "swiglu":
+            self.gate = nn.Linear(dim, ffn, bias=False, device=device)
+            self.up = nn.Linear(dim, ffn, bias=False, device=device)
+            self.down = nn.Linear(ffn, dim, bias=False, device=device)
+            self.act = nn.SiLU()
+        else:
+            self.fc = nn.Linear(dim, ffn, device=device)
+            self.proj = nn.Linear(ffn, dim, device=device)
+            self.act = nn.GELU()
+        self.gated = spec["mlp"] == "swiglu"
+
+    def forward(self, x):
+        if self.gated:
+            return self.down(self.act(self.gate(x)) * self.up(x))
+        return self.proj(self.act(self.fc(x)))
+
+
+class DecoderAttention(nn.Module):
+    def __init__(self, spec, device):
+        super().__init__()
+        dim, self.heads, self.kv_heads = spec["dim"], spec["heads"], spec["kv_heads"]
+        self.head_dim = dim // self.heads
+        bias = spec["norm"] == "layer"
+        self.qkv = nn.Linear(dim, (self.heads + 2 * self.kv_heads) * self.head_dim, bias=bias, device=device)
+        self.out = nn.Linear(dim, dim, bias=bias, device=device)
+        self.rope = spec["rope"]
+
+    def forward(self, x, rotary):
+        batch, seq, _ = x.shape
+        q, k, v = self.qkv(x).split([self.heads * self.head_dim, self.kv_heads * self.head_dim,
+                                     self.kv_heads * self.head_dim], dim=-1)
+        q = q.view(batch, seq, self.heads, self.head_dim).transpose(1, 2)
+        k = k.view(batch, seq, self.kv_heads, self.head_dim).transpose(1, 2)
+        v = v.view(batch, seq, self.kv_heads, self.head_dim).transpose(1, 2)
+        if self.rope:
+            cos, sin = rotary
+            q = q * cos + torch.cat((-q[..., self.head_dim // 2:], q[..., : self.head_dim // 2]), -1) * sin
+            k = k * cos + torch.cat((-k[..., self.head_dim // 2:], k[..., : self.head_dim // 2]), -1) * sin
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.heads != self.kv_heads)
+        return self.out(y.transpose(1, 2).reshape(batch, seq, -1))
+
+
+class DecoderBlock(nn.Module):
+    def __init__(self, spec, device):
+        super().__init__()
+        make = (lambda: nn.LayerNorm(spec["dim"], device=device)) if spec["norm"] == "layer" \
+            else (lambda: nn.RMSNorm(spec["dim"], device=device))
+        self.norm1, self.norm2 = make(), make()
+        self.attention = DecoderAttention(spec, device)
+        self.mlp = DecoderMLP(spec, device)
+
+    def forward(self, x, rotary):
+        x = x + self.attention(self.norm1(x), rotary)
+        return x + self.mlp(self.norm2(x))
+
+
+class Decoder(nn.Module):
+    def __init__(self, spec, device):
+        super().__init__()
+        self.spec = spec
+        self.embed = nn.Embedding(spec["vocab"], spec["dim"], device=device)
+        self.positions = None if spec["rope"] else nn.Embedding(spec["seq"], spec["dim"], device=device)
+        self.blocks = nn.ModuleList([DecoderBlock(spec, device) for _ in range(spec["layers"])])
+        self.norm = nn.LayerNorm(spec["dim"], device=device) if spec["norm"] == "layer" else nn.RMSNorm(spec["dim"], device=device)
+        self.head = nn.Linear(spec["dim"], spec["vocab"], bias=False, device=device)
+        if spec["tied_head"]:
+            self.head.weight = self.embed.weight
+        if spec["rope"]:
+            half = spec["dim"] // spec["heads"] // 2
+            frequency = 1.0 / (10000.0 ** (torch.arange(half, device=device, dtype=torch.float32) / half))
+            angle = torch.outer(torch.arange(spec["seq"], device=device, dtype=torch.float32), frequency)
+            angle = torch.cat((angle, angle), -1)
+            self.register_buffer("cos", angle.cos()[None, None], persistent=False)
+            self.register_buffer("sin", angle.sin()[None, None], persistent=False)
+
+    def forward(self, ids):
+        x = self.embed(ids)
+        rotary = None
+        if self.positions is not None:
+            x = x + self.positions(torch.arange(ids.shape[1], device=ids.device))
+        else:
+            rotary = (self.cos[:, :, : ids.shape[1]].to(x.dtype), self.sin[:, :, : ids.shape[1]].to(x.dtype))
+        for block in self.blocks:
+            x = block(x, rotary)
+        return self.head(self.norm(x))
+
+
+def run_decoder(args) -> dict:
+    """configs[2] / configs[3]: a decoder trained with only its MLPs converted.  One step = the
+    job's global batch (forward, backward, AdamW on the float parameters, QSTEOptimizer on the
+    coordinates); a rank whose share is more than one micro-batch of 8 sequences accumulates with
+    `QSTEOptimizer.prepare_accumulation()` and applies the summed evidence once per step."""
+
+    import qste_b200 as qste
+    from qste_b200 import distributed as qdist
+    from qste_b200 import kernels
+
+    spec = DECODERS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    if spec["global_batch"] % world:
+        raise SystemExit(f"{args.workload}: global batch {spec['global_batch']} does not divide over {world} GPUs")
+    per_rank = spec["global_batch"] // world
+    micro = min(spec["micro_batch"], per_rank)
+    micro_steps = per_rank // micro
+    seq = spec["seq"]
+
+    torch.manual_seed(1234)
+    model = Decoder(spec, device)
+    qste.convert(model, include=spec["include"])
+    reducer = qdist.mean_evidence(overlap=True, reserve_sms=args.reserve if args.reserve >= 0 else None) if world > 1 else None
+    coordinates = qste.QSTEOptimizer(model, gradient_reducer=reducer if reducer else False, async_update=micro_steps == 1)
+    if micro_steps > 1:
+        coordinates.prepare_accumulation()
+    floats = list(qste.continuous_parameters(model))
+    host_optimizer = torch.optim.AdamW(floats, lr=1e-4, fused=True)
+    wrapped = model
+    if world > 1:
+        from torch.nn.parallel import DistributedDataParallel
+
+        # float parameters (attention, norms, embeddings, row scales, biases) ride DDP's buckets; the
+        # coordinate evidence is not an autograd gradient and goes through the evidence reducer
+        wrapped = DistributedDataParallel(model, device_ids=[local], gradient_as_bucket_view=True)
+
+    generator = torch.Generator().manual_seed(1000 + rank)
+    pinned = [torch.randint(0, spec["vocab"], (per_rank, seq + 1), generator=generator).pin_memory() for _ in range(2)]
+    resident = [batch.to(device) for batch in pinned]
+    counter = {"step": 0, "flips": 0}
+
+    def step(ids):
+        total = None
+        for index in range(micro_steps):
+            chunk = ids[index * micro:(index + 1) * micro]
+            last = index == micro_steps - 1
+            context = wrapped.no_sync() if (world > 1 and not last) else nullcontext()
+            with context:
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    logits = wrapped(chunk[:, :-1])
+                loss = F.cross_entropy(logits.float().view(-1, logits.shape[-1]), chunk[:, 1:].reshape(-1)) / micro_steps
+                loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        host_optimizer.step()
+        counter["flips"] += coordinates.step()
+        host_optimizer.zero_grad(set_to_none=True)
+        if micro_steps == 1:
+            coordinates.zero_grad()
+        counter["step"] += 1
+        return total
+
+    def resident_step():
+        step(resident[counter["step"] % 2])
+
+    def e2e_step():
+        ids = pinned[counter["step"] % 2].to(device, non_blocking=True)
+        return float(step(ids).item())
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        resident_step()
+    barrier()
+    launches_before = launch_count()
+    with ClockSampler(local) as clocks:
+        seconds = timed(resident_step, args.steps)
+    launches = launch_count() - launches_before
+    barrier()
+    seconds = max_over_ranks(seconds, world, device)
+    e2e_step()
+    barrier()
+    e2e_seconds = max_over_ranks(timed(e2e_step, args.steps), world, device)
+
+    tokens_per_step = spec["global_batch"] * seq
+    mlp_rows = micro * seq
+    result = {
+        "metric": METRIC, "value": tokens_per_step * args.steps / seconds, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / args.steps,
+        "higher_is_better": True, "scaling": "strong" if spec["global_batch"] > spec["micro_batch"] else "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
+        "config": {"workload": f"{args.workload}: {spec['layers']} layers, d={spec['dim']}, ffn={spec['ffn']}, "
+                               f"{spec['heads']}/{spec['kv_heads']} heads, vocab {spec['vocab']}, seq {seq}, global batch "
+                               f"{spec['global_batch']} sequences, MLPs converted ({len(coordinates.surfaces)} surfaces), "
+                               f"bf16 autocast",
+                   "parallelism": f"dp{world}", "sequences_per_gpu": per_rank, "micro_batches_per_step": micro_steps,
+                   "l2": "each step's activations exceed L2 many times over; two rotating token batches"},
+        "e2e": {"value": tokens_per_step * args.steps / e2e_seconds, "unit": "tokens/s",
+                "h2d_bytes_per_step": per_rank * (seq + 1) * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches, "clocks": clocks.summary(),
+        "flips_per_step": counter["flips"] / max(1, counter["step"]),
+        "wait_timeouts": kernels.wait_timeouts(device), "ranks_agree": bool(qdist.surfaces_agree(model)),
+    }
+    if rank == 0 and not args.no_extras:
+        torch.cuda.synchronize()
+        time.sleep(3.0)
+        result["roofline"] = kernel_roofline(device, mlp_rows, spec["dim"], spec["ffn"])
+        if world == 1:
+            result["cpu_baseline"] = decoder_cpu_baseline(spec, mlp_rows, tokens_per_step)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def run_decoder_reference(args) -> dict:
+    """`--impl reference` for a decoder workload: the per-block CPU figure of decoder_cpu_baseline
+    as the arm's line (the MLP blocks are the path; the rest of the model is not run on the CPU)."""
+
+    if int(os.environ.get("RANK", "0")) != 0:
+        return {}
+    try:
+        torch.set_num_threads(max(torch.get_num_threads(), len(os.sched_getaffinity(0))))
+    except (AttributeError, RuntimeError):
+        pass
+    spec = DECODERS[args.workload]
+    mlp_rows = min(spec["micro_batch"], spec["global_batch"]) * spec["seq"]
+    baseline = decoder_cpu_baseline(spec, mlp_rows, spec["global_batch"] * spec["seq"])
+    return {"impl": "reference", "metric": METRIC, "value": baseline["value"], "unit": "tokens/s",
+            "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": 1, "warmup": 0,
+            "ms_per_step": 1e3 * baseline["seconds_per_block_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: converted MLP blocks only, on the CPU; ms_per_step is ONE block at "
+                                   f"{mlp_rows} tokens, value = tokens / ({spec['layers']} layers x block time)"},
+            "cpu_baseline": baseline,
+            "e2e": {"value": baseline["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def decoder_cpu_baseline(spec, mlp_rows: int, tokens_per_step: int) -> dict:
+    """The reference's CPU kernels on ONE converted MLP block of the decoder at a micro-batch's
+    full token count: forward, backward and the block's coordinate updates.  Attention, norms,
+    embeddings and the head are not on the path and are not run, so tokens/s = tokens / (layers x
+    block time) bounds the CPU's whole-model figure from above."""
+
+    if spec["mlp"] == "swiglu":
+        times, _, split, kind = cpu_block_steps(mlp_rows, 1, 0, dim=spec["dim"], ffn=spec["ffn"])
+    else:
+        times, split, kind = cpu_plain_mlp_steps(mlp_rows, spec["dim"], spec["ffn"])
+    seconds = statistics.median(times)
+    return {"value": mlp_rows / (seconds * spec["layers"]), "unit": "tokens/s", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": kind,
+            "sample": f"one converted MLP block (d={spec['dim']}, ffn={spec['ffn']}) x {mlp_rows} tokens, fp32, forward + "
+                      f"backward + coordinate updates, 1 step; MLP blocks only (attention, embeddings and head are not "
+                      f"run): tokens/s = tokens / ({spec['layers']} layers x block time), an upper bound for the CPU",
+            "seconds_per_block_step": seconds, "seconds_by_call": {key: round(value, 3) for key, value in split.items()}}
+
+
+def cpu_plain_mlp_steps(tokens: int, dim: int, ffn: int):
+    """One fc -> GELU -> proj block on the CPU through the reference's kernels, one step."""
+
+    k, kind = _cpu_kernels()
+    generator = torch.Generator().manual_seed(6)
+    clock: dict = {}
+    fc = CpuBinaryLinear(k, ffn, dim, generator, 0, clock)
+    proj = CpuBinaryLinear(k, dim, ffn, generator, 1, clock)
+    x = torch.randn(tokens, dim, generator=generator)
+    begin = time.perf_counter()
+    h = fc.forward(x)
+    a = F.gelu(h)
+    y = proj.forward(a)
+    dy = y * (2.0 / y.numel())
+    da, _, _ = proj.backward(dy, 0)
+    cdf = 0.5 * (1.0 + torch.erf(h * 0.7071067811865476))
+    dh = da * (cdf + h * torch.exp(-0.5 * h * h) * 0.3989422804014327)
+    fc.backward(dh, 0)
+    seconds = time.perf_counter() - begin
+    clock["harness_elementwise"] = seconds - sum(clock.values())
+    return [seconds], dict(clock), kind
 
 
 # ------------------------------------------------------------------------------------------
@@ -732,12 +1036,182 @@ def run_sweep(args) -> dict:
                 entry["forward"]["timing"] = f"CUDA graph of {copies} launches over {copies} weight copies"
             rows.append(entry)
     value = total_flops / total_seconds / 1e12
-    return {"metric": "packed_sign_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
+    best = max((r for r in rows if r["m"] >= 4096), key=lambda r: r["forward"]["tflops"])
+    small = [r for r in rows if r["m"] <= 128]
+    extras = {
+        "roofline": {"bound": "tensor", "kernel": f"packed-sign forward GEMM, M={best['m']}, K={best['k']}, N={best['n']}",
+                     "achieved": best["forward"]["tflops"], "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": best["forward"]["tflops"] / peak["bf16_tflops"], "peak_source": peak["source"], "traffic": None,
+                     "small_batch_hbm": {f"m{r['m']}_k{r['k']}_n{r['n']}": round(r["forward"]["frac_hbm"], 4) for r in small}},
+    }
+    if not args.no_extras:
+        extras["cpu_baseline"] = sweep_cpu_baseline()
+    return {**extras, "metric": "packed_sign_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "packed-sign GEMM sweep, forward + dX + evidence, M in {1,16,128,4096,16384} x "
                                    "4 (K,N); value = flop-weighted mean over M >= 4096"},
             "frac_tensor_peak": value / peak["bf16_tflops"], "sweep": rows}
+
+
+def sweep_cpu_baseline(repeats: int = 3) -> dict:
+    """configs[1] on the CPU through the reference's kernels (fp32: the reference up-casts bf16
+    on the CPU): forward, dX and evidence at every (K, N) for M in {1, 16, 128}, and at
+    M in {4096, 16384} for (4096, 14336); median of `repeats`."""
+
+    k_ref, kind = _cpu_kernels()
+    rows = []
+    generator = torch.Generator().manual_seed(2)
+    for k, n in SWEEP_SHAPES:
+        packed = torch.randint(0, 256, (n, k // 8), generator=generator, dtype=torch.int32).to(torch.uint8)
+        scale = torch.rand(n, generator=generator) * 0.04 + 0.01
+        for m in SWEEP_BATCHES:
+            if m > 128 and (k, n) != (D_MODEL, D_FFN):
+                continue
+            x = torch.randn(m, k, generator=generator)
+            dy = torch.randn(m, n, generator=generator)
+            bits, _, act_scale = k_ref.pack_affine_rows(x)
+            entry = {"m": m, "k": k, "n": n}
+            for name, call in (("forward", lambda: k_ref.packed_linear_affine(x, packed, scale, None, k)),
+                               ("dx", lambda: k_ref.packed_transpose(dy, packed, k, scale)),
+                               ("evidence", lambda: k_ref.evidence_from_packed(dy, bits, k, act_scale))):
+                times = []
+                for _ in range(repeats):
+                    begin = time.perf_counter()
+                    call()
+                    times.append(time.perf_counter() - begin)
+                seconds = statistics.median(times)
+                entry[name] = {"us": seconds * 1e6, "tflops": 2.0 * m * k * n / seconds / 1e12}
+            rows.append(entry)
+    large = [r for r in rows if r["m"] >= 4096]
+    flops = sum(3 * 2.0 * r["m"] * r["k"] * r["n"] for r in large)
+    seconds = sum((r["forward"]["us"] + r["dx"]["us"] + r["evidence"]["us"]) * 1e-6 for r in large)
+    return {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": kind,
+            "sample": f"fp32, median of {repeats}: all four (K,N) at M in {{1,16,128}}; M in {{4096,16384}} at (4096,14336) "
+                      "only; value = flop-weighted mean over those large-M rows",
+            "rows": rows}
+
+
+def run_layer(args) -> dict:
+    """configs[0]: one converted Linear, R = C = 2048, batch 256, fp32.  A step is one forward,
+    one backward with an N(0,1) upstream gradient, one QSTEOptimizer step and one AdamW step on
+    the row scales and the bias; `--impl reference` runs the same step on the CPU through the
+    reference's kernels.  Value = steps per second of the median step (at least ten are timed)."""
+
+    import numpy as np
+
+    rows = columns = 2048
+    batch = 256
+    steps = max(10, args.steps)
+    generator = torch.Generator().manual_seed(1)
+    coordinate = torch.randint(-127, 128, (rows, columns), generator=generator, dtype=torch.int32).to(torch.int8)
+    x = torch.randn(batch, columns, generator=generator)
+    dy = torch.randn(batch, rows, generator=generator)
+    config = {"workload": "single converted Linear, R=C=2048, batch 256, fp32: forward + backward + QSTEOptimizer step + "
+                          "AdamW step on scale and bias", "l2": "the step's 17 MB evidence and 4 MB state fit L2: a latency-bound case"}
+    common = {"metric": "converted_linear_steps_per_s", "unit": "steps/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+              "config": config}
+    if args.impl == "reference":
+        k_ref, kind = _cpu_kernels()
+        clock: dict = {}
+        layer = CpuBinaryLinear(k_ref, rows, columns, generator, 0, clock)
+        layer.coordinate.copy_(coordinate)
+        layer.packed = k_ref.pack_coordinate(layer.coordinate)
+        log_scale = torch.full((rows,), float(np.log(0.02)), requires_grad=True)
+        bias = torch.zeros(rows, requires_grad=True)
+        host = torch.optim.AdamW([log_scale, bias], lr=1e-3)
+        times = []
+        for number in range(args.warmup + steps):
+            begin = time.perf_counter()
+            layer.scale = log_scale.detach().exp()
+            y = layer.forward(x) + bias.detach()
+            _, g_scale, _ = layer.backward(dy, number)
+            log_scale.grad = g_scale * layer.scale
+            bias.grad = dy.sum(0)
+            host.step()
+            if number >= args.warmup:
+                times.append(time.perf_counter() - begin)
+        seconds = statistics.median(times)
+        del y
+        return dict(common, impl="reference", value=1.0 / seconds, ms_per_step=1e3 * seconds,
+                    cpu_baseline={"value": 1.0 / seconds, "unit": "steps/s", "cores": torch.get_num_threads(), "kind": kind,
+                                  "sample": f"the whole step, median of {steps}"},
+                    e2e={"value": 1.0 / seconds, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+
+    import qste_b200 as qste
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    surface = qste.Surface(torch.zeros(rows, columns)).to(device)
+    with torch.no_grad():
+        surface.coordinate.copy_(coordinate)
+        surface.refresh_packed()
+        surface.log_scale.fill_(float(np.log(0.02)))
+    layer = qste.QSTELinear(surface, torch.zeros(rows)).to(device)
+    coordinates = qste.QSTEOptimizer([surface])
+    host = torch.optim.AdamW(list(layer.parameters()), lr=1e-3, fused=True)
+    xd, dyd = x.to(device), dy.to(device)
+    x_pinned, dy_pinned = x.pin_memory(), dy.pin_memory()
+
+    def step(inputs, upstream):
+        layer(inputs).backward(upstream)
+        host.step()
+        flips = coordinates.step()
+        host.zero_grad(set_to_none=True)
+        coordinates.zero_grad()
+        return flips
+
+    def timed_steps(fn):
+        times = []
+        for number in range(args.warmup + steps):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            if number >= args.warmup:
+                times.append(begin.elapsed_time(end) / 1e3)
+        return statistics.median(times)
+
+    launches_before = launch_count()
+    with ClockSampler(0) as clocks:
+        seconds = timed_steps(lambda: step(xd, dyd))
+    launches = (launch_count() - launches_before) * steps // (args.warmup + steps)
+    e2e_seconds = timed_steps(lambda: step(x_pinned.to(device, non_blocking=True), dy_pinned.to(device, non_blocking=True)))
+    result = dict(common, value=1.0 / seconds, ms_per_step=1e3 * seconds, gpu_launches=launches, clocks=clocks.summary(),
+                  e2e={"value": 1.0 / e2e_seconds, "unit": "steps/s", "h2d_bytes_per_step": (x.numel() + dy.numel()) * 4,
+                       "d2h_bytes_per_step": 8})
+    # the step's dominant kernel by bytes: the coordinate update of 4.2 M coordinates
+    from qste_b200 import kernels
+
+    state = coordinates.state[id(surface)]
+    evidence = torch.randn(rows, columns, device=device)
+    scratch = torch.empty_like(evidence)
+    flips = torch.zeros((), dtype=torch.int64, device=device)
+
+    def update():
+        scratch.copy_(evidence)
+        kernels.coordinate_update(scratch, surface.coordinate.data, surface.packed_sign.data, state["moment_q"],
+                                  state["moment_scale"], state["row_v"], state["col_v"], beta1=0.9, beta2=0.99,
+                                  update_clip=2.0, coordinate_lr=1.0, block_size=256, seed=1, step=0, flips=flips)
+
+    update()
+    copy_seconds = timed(lambda: scratch.copy_(evidence), 20) / 20
+    update_seconds = timed(update, 20) / 20 - copy_seconds
+    peak = peaks()
+    achieved = 8.125 * rows * columns / update_seconds / 1e9
+    result["roofline"] = {"bound": "hbm", "kernel": "coordinate_update (9 launches), 2048 x 2048", "achieved": achieved,
+                          "peak": peak["hbm_gbs"], "unit": "GB/s", "frac": achieved / peak["hbm_gbs"],
+                          "peak_source": peak["source"], "traffic": None, "us_per_launch": update_seconds * 1e6,
+                          "note": "compulsory bytes (8.125 per coordinate) over the time of the whole update; at this "
+                                  "size the state fits L2 and the nine dependent launches bound it, not DRAM"}
+    if not args.no_extras:
+        reference = run_layer(argparse.Namespace(**{**vars(args), "impl": "reference"}))
+        result["cpu_baseline"] = dict(reference["cpu_baseline"], ms_per_step=reference["ms_per_step"])
+    return result
 
 
 def run_kernel(args) -> dict:
@@ -789,7 +1263,8 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="mlp_stack", choices=["mlp_stack", "gemm_sweep", "kernel"])
+    parser.add_argument("--workload", default="mlp_stack",
+                        choices=["mlp_stack", "gemm_sweep", "layer_2048", "gpt2_small", "llama_1b", "kernel"])
     parser.add_argument("--kernel", default="forward", choices=["forward", "dx", "evidence", "backward", "pack", "pack_coordinate", "row_inner", "update"],
                         help="with --workload kernel: which kernel to launch")
     parser.add_argument("--no-extras", action="store_true",
@@ -799,12 +1274,26 @@ def main() -> None:
                         help="SMs the backward GEMMs leave to the all-reduce at N > 1 (default: the library's, 8)")
     parser.add_argument("--blocks", type=int, default=0, help="SwiGLU blocks (default 8)")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.workload == "layer_2048":
+        result = run_layer(args)
+    elif args.impl == "reference" and args.workload in DECODERS:
+        result = run_decoder_reference(args)
+    elif args.impl == "reference" and args.workload == "gemm_sweep":
+        baseline = sweep_cpu_baseline() if int(os.environ.get("RANK", "0")) == 0 else None
+        result = {} if baseline is None else {
+            "impl": "reference", "metric": "packed_sign_gemm_tflops", "value": baseline["value"], "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": 3, "warmup": 0, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": "packed-sign GEMM sweep on the CPU: " + baseline["sample"]},
+            "cpu_baseline": baseline,
+            "e2e": {"value": baseline["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    elif args.impl == "reference":
         result = run_reference(args)
     elif args.workload == "gemm_sweep":
         result = run_sweep(args)
     elif args.workload == "kernel":
         result = run_kernel(args)
+    elif args.workload in DECODERS:
+        result = run_decoder(args)
     else:
         result = run_ours(args)
     if result:

@@ -56,7 +56,8 @@ typedef enum {
   QSTE_PATH_AUTO = 0,   /* tcgen05 tensor-core kernel when the shape allows it, else the others */
   QSTE_PATH_SIMT = 1,   /* generic CUDA-core kernel (any shape) */
   QSTE_PATH_TENSOR = 2, /* tcgen05/TMEM kernel; QSTE_ERR_UNSUPPORTED when the shape does not fit */
-  QSTE_PATH_STREAM = 3  /* small-batch packed-bit streaming kernel (forward only) */
+  QSTE_PATH_STREAM = 3, /* packed-bit streaming kernel on the CUDA cores, batches of 1-4 (forward only) */
+  QSTE_PATH_SMALL = 4   /* weight-stationary tcgen05 kernel, batches of 1-128, bf16/fp16 (forward only) */
 } qste_path;
 
 int qste_b200_abi_version(void);
@@ -216,6 +217,33 @@ int qste_b200_packed_row_inner(const float* matrix, const uint8_t* packed, int64
 int qste_b200_packed_embedding(const int64_t* ids, int64_t count, const uint8_t* packed,
                                const float* scale, int64_t rows, int64_t columns, void* out,
                                int out_dtype, int32_t* bad_id, qste_stream_t stream);
+
+/* ---- packed activations ----------------------------------------------------- */
+
+/* Smooth activation with an int8 derivative tape, forward: for every row of `inputs`
+ * ([rows, columns] of `dtype`, row-major, contiguous)
+ *   outputs    = f(inputs)                                     (same dtype)
+ *   scale[r]   = max(max_c |f'(inputs[r, c])|, 1e-8) / 127     (fp32)
+ *   derivative = clamp(rint(f'(inputs) / scale[r]), -127, 127) (int8 [rows, columns])
+ * in one pass over the row.  `kind` is a qste_activation; `parameter` is alpha (ELU, CELU) or
+ * beta (Softplus) and ignored otherwise.  columns * 4 bytes must fit in shared memory
+ * (QSTE_ERR_LIMIT beyond 51200 columns).
+ * Reference: _SmoothFn.forward, src/qste/nn.py:483-502, with the derivatives of :392-470. */
+typedef enum {
+  QSTE_ACT_GELU = 0, QSTE_ACT_GELU_TANH = 1, QSTE_ACT_SILU = 2, QSTE_ACT_TANH = 3,
+  QSTE_ACT_SIGMOID = 4, QSTE_ACT_ELU = 5, QSTE_ACT_CELU = 6, QSTE_ACT_SELU = 7,
+  QSTE_ACT_SOFTPLUS = 8, QSTE_ACT_MISH = 9, QSTE_ACT_HARDSWISH = 10
+} qste_activation;
+int qste_b200_smooth_forward(const void* inputs, int dtype, int64_t rows, int64_t columns, int kind,
+                             double parameter, void* outputs, int8_t* derivative, float* scale,
+                             qste_stream_t stream);
+
+/* ... and backward: grad_inputs = grad * (derivative * scale[r]), each product rounded to
+ * `dtype` as the reference's torch expression rounds it.
+ * Reference: _SmoothFn.backward, src/qste/nn.py:504-507. */
+int qste_b200_smooth_backward(const void* grad, int dtype, const int8_t* derivative,
+                              const float* scale, int64_t rows, int64_t columns, void* grad_inputs,
+                              qste_stream_t stream);
 
 /* ---- coordinate optimizer --------------------------------------------------- */
 

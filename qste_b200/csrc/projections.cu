@@ -2,6 +2,8 @@
 // evidence side of the Linear backward.  Chooses between the tcgen05 kernel
 // (gemm_tc.cu), the CUDA-core kernel and the small-batch streaming kernel
 // (gemm_simt.cu).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemm.h"
 
@@ -12,6 +14,13 @@ namespace {
 constexpr size_t kHeader = 256;  // workspace[0..8): device wait-timeout counter
 
 inline bool valid_dtype(int dtype) { return dtype_size(dtype) != 0; }
+
+// QSTE_B200_SMALL_BATCH=0 keeps batches of 1-128 on the kernels that served them before the
+// weight-stationary one existed (for A/B timing).
+inline bool small_batch_auto() {
+  static const bool enabled = !(getenv("QSTE_B200_SMALL_BATCH") && atoi(getenv("QSTE_B200_SMALL_BATCH")) == 0);
+  return enabled;
+}
 
 }  // namespace
 
@@ -35,6 +44,14 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
   cudaStream_t s = as_stream(stream);
   const int64_t pitch = (columns + 7) / 8;
 
+  if (path == QSTE_PATH_SMALL ||
+      (path == QSTE_PATH_AUTO && small_batch_auto() && ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype) &&
+       ws_preferred(samples, rows, columns))) {
+    if (!ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype)) return QSTE_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < kHeader) return QSTE_ERR_WORKSPACE;
+    return ws_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, out_dtype,
+                      static_cast<unsigned long long*>(workspace), s);
+  }
   if (path == QSTE_PATH_STREAM ||
       (path == QSTE_PATH_AUTO && stream_single_launch(samples, columns) &&
        stream_supported(samples, rows, columns, packed))) {

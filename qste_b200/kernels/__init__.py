@@ -23,12 +23,13 @@ from . import _cabi, stream
 from .device import DeviceProfile, profile, warm
 
 _DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
-PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_STREAM = 0, 1, 2, 3
-_PATH_NAMES = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tensor": PATH_TENSOR, "stream": PATH_STREAM}
+PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_STREAM, PATH_SMALL = 0, 1, 2, 3, 4
+_PATH_NAMES = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tensor": PATH_TENSOR, "stream": PATH_STREAM,
+               "small": PATH_SMALL}
 
 
 def _path() -> int:
-    """``QSTE_B200_PATH=auto|simt|tensor|stream`` pins the GEMM implementation (for tests)."""
+    """``QSTE_B200_PATH=auto|simt|tensor|stream|small`` pins the GEMM implementation (for tests)."""
 
     name = os.environ.get("QSTE_B200_PATH", "auto").strip().lower()
     if name not in _PATH_NAMES:
@@ -543,6 +544,58 @@ def packed_embedding(ids: Tensor, packed: Tensor, scale: Tensor, columns: int) -
     return out.view(*ids.shape, columns).to(scale.dtype)
 
 
+# -- packed activations -------------------------------------------------------------
+
+SMOOTH_KINDS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "tanh": 3, "sigmoid": 4, "elu": 5, "celu": 6,
+                "selu": 7, "softplus": 8, "mish": 9, "hardswish": 10}
+_SMOOTH_MAX_COLUMNS = 51200  # the row's derivatives sit in shared memory as fp32
+
+
+def smooth_supported(inputs: Tensor) -> bool:
+    """Whether :func:`smooth_forward` takes this tensor (else the caller composes torch ops)."""
+
+    return inputs.is_cuda and inputs.dtype in _DTYPES and inputs.dim() >= 1 and \
+        0 < inputs.shape[-1] <= _SMOOTH_MAX_COLUMNS and inputs.numel() > 0
+
+
+def smooth_forward(inputs: Tensor, kind: str, parameter: float = 1.0) -> tuple[Tensor, Tensor, Tensor]:
+    """``(f(x), int8 derivative, fp32 row scale)`` of a smooth activation in one pass over
+    ``x`` (rows are taken over the last dimension).  The forward half of the reference's
+    ``_SmoothFn`` (src/qste/nn.py:483-502) as one kernel; no counterpart in its kernel namespace."""
+
+    _need_cuda(inputs, "smooth_forward")
+    code = _dtype(inputs, "smooth_forward")
+    columns = inputs.shape[-1]
+    flat = inputs.reshape(-1, columns).contiguous()
+    rows = flat.shape[0]
+    outputs = torch.empty_like(flat)
+    derivative = torch.empty(rows, columns, dtype=torch.int8, device=flat.device)
+    scale = torch.empty(rows, dtype=torch.float32, device=flat.device)
+    with torch.cuda.device(flat.device):
+        _cabi.check(_cabi.load().qste_b200_smooth_forward(
+            _ptr(flat), code, rows, columns, SMOOTH_KINDS[kind], float(parameter), _ptr(outputs), _ptr(derivative),
+            _ptr(scale), _stream(flat.device)), "smooth_forward")
+    return outputs.view(inputs.shape), derivative, scale
+
+
+def smooth_backward(grad: Tensor, derivative: Tensor, scale: Tensor) -> Tensor:
+    """``grad * (derivative * scale)`` (src/qste/nn.py:504-507 of the reference) as one kernel."""
+
+    _need_cuda(grad, "smooth_backward")
+    rows, columns = derivative.shape
+    if grad.numel() != rows * columns or scale.numel() != rows or derivative.dtype != torch.int8:
+        raise RuntimeError("smooth_backward: gradient, derivative tape and scale do not match")
+    if grad.dtype not in _DTYPES:
+        return smooth_backward(grad.float(), derivative, scale).to(grad.dtype)
+    flat = grad.reshape(rows, columns).contiguous()
+    out = torch.empty_like(flat)
+    with torch.cuda.device(flat.device):
+        _cabi.check(_cabi.load().qste_b200_smooth_backward(
+            _ptr(flat), _DTYPES[flat.dtype], _ptr(derivative.contiguous()), _ptr(_f32(scale)), rows, columns, _ptr(out),
+            _stream(flat.device)), "smooth_backward")
+    return out.view(grad.shape)
+
+
 # -- optimizer --------------------------------------------------------------------
 
 def _check_update_arguments(what, gradient, coordinate, packed, moment_q, moment_scale, row_v, col_v,
@@ -703,6 +756,7 @@ __all__ = [
     "DeviceProfile", "apply_bits", "coordinate_update", "coordinate_update_static", "cuda_available", "cuda_backend",
     "evidence_from_packed", "linear_backward", "linear_backward_evidence", "native_available", "pack_bits",
     "pack_coordinate", "pack_affine_rows", "packed_embedding", "packed_linear_affine",
-    "packed_row_inner", "packed_transpose", "profile", "set_backward_reserve", "status", "stream", "unpack_bits",
+    "packed_row_inner", "packed_transpose", "profile", "set_backward_reserve", "smooth_backward", "smooth_forward",
+    "smooth_supported", "status", "stream", "unpack_bits",
     "unpack_rows", "wait_timeouts", "warm", "warn_if_slow", "first_wait_timeout", "check_waits",
 ]

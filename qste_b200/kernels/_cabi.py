@@ -37,6 +37,8 @@ SYMBOLS = (
     "qste_b200_linear_backward_staged",
     "qste_b200_packed_row_inner",
     "qste_b200_packed_embedding",
+    "qste_b200_smooth_forward",
+    "qste_b200_smooth_backward",
     "qste_b200_coordinate_update_workspace",
     "qste_b200_coordinate_update",
     "qste_b200_coordinate_update_static",
@@ -80,6 +82,8 @@ _SIGNATURES = {
         _int, [_p, _int, _i64, _i64, _p, _p, _i64, _p, _p, _p, _int, _p, _p, _p, _p, _p, _size, _p]),
     "qste_b200_packed_row_inner": (_int, [_p, _p, _i64, _i64, _p, _p]),
     "qste_b200_packed_embedding": (_int, [_p, _i64, _p, _p, _i64, _i64, _p, _int, _p, _p]),
+    "qste_b200_smooth_forward": (_int, [_p, _int, _i64, _i64, _int, _f64, _p, _p, _p, _p]),
+    "qste_b200_smooth_backward": (_int, [_p, _int, _p, _p, _i64, _i64, _p, _p]),
     "qste_b200_coordinate_update_workspace": (_size, [_i64, _i64, _i64]),
     "qste_b200_coordinate_update": (
         _int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f64, _f64, _f64, _f64, _i64, _i64, _i64,

@@ -58,13 +58,11 @@ _TORCH_HARDSWISH = F.hardswish
 
 
 def _rows(value: Tensor) -> tuple[Tensor, torch.Size, int]:
-    """Rank-2 contiguous view over the last dimension (packing is per row)."""
+    """``(matrix, original shape, columns)``: the tensor as contiguous rows over its last
+    dimension, which is what the bit and int8 tapes are packed along.  A scalar counts as one
+    row of one column, a vector as one row."""
 
-    if value.ndim == 0:
-        return value.reshape(1, 1).contiguous(), value.shape, 1
-    if value.ndim == 1:
-        return value.reshape(1, -1).contiguous(), value.shape, value.shape[0]
-    columns = value.shape[-1]
+    columns = value.shape[-1] if value.ndim else 1
     return value.reshape(-1, columns).contiguous(), value.shape, columns
 
 
@@ -322,11 +320,32 @@ _SMOOTH = {
 }
 
 
+def _fused_kind(kind: str, approximate) -> tuple[str, float] | None:
+    """(kernel kind, parameter) when the library's one-pass kernel covers this activation."""
+
+    if kind == "gelu":
+        return ("gelu_tanh", 1.0) if approximate == "tanh" else ("gelu", 1.0)
+    if kind in ("elu", "celu", "softplus"):
+        return kind, float(approximate)
+    return (kind, 1.0) if kind in kernels.SMOOTH_KINDS else None
+
+
 class _SmoothFn(Function):
-    """Forward is torch's; the local derivative is retained as int8 + a row scale."""
+    """The local derivative is retained as int8 + a row scale (nn.py:483-507 of the reference).
+
+    On the GPU forward is ONE library kernel (``kernels.smooth_forward``: activation, derivative,
+    row maximum and int8 tape in a single pass over the input) and backward another; elsewhere
+    the same arithmetic is composed from torch operations."""
 
     @staticmethod
     def forward(ctx, inputs, kind, approximate):
+        fused = _fused_kind(kind, approximate) if kernels.smooth_supported(inputs) else None
+        ctx.fused = fused is not None
+        if fused is not None:
+            output, payload, scale = kernels.smooth_forward(inputs, *fused)
+            ctx.save_for_backward(payload, scale)
+            ctx.shape = inputs.shape
+            return output
         forward, derivative_of = _SMOOTH[kind]
         output = forward(inputs, approximate)
         derivative = derivative_of(inputs.float(), output.float(), approximate)
@@ -340,6 +359,8 @@ class _SmoothFn(Function):
     @staticmethod
     def backward(ctx, grad_output):
         payload, scale = ctx.saved_tensors
+        if ctx.fused and grad_output.is_cuda:
+            return kernels.smooth_backward(grad_output, payload, scale), None, None
         derivative = payload.to(grad_output.dtype).mul_(scale.to(grad_output.dtype).unsqueeze(1))
         return grad_output * derivative.view(ctx.shape), None, None
 
@@ -578,25 +599,22 @@ SMOOTH_REPLACEMENTS: dict[type, type] = {
 REPLACEMENTS: dict[type, type] = {**EXACT_REPLACEMENTS, **SMOOTH_REPLACEMENTS}
 
 
-def replace(module: nn.Module) -> nn.Module | None:
-    """The packed twin of ``module`` with its hyper-parameters, or ``None``."""
+# hyper-parameters a twin takes over from the module it replaces, in constructor order
+_CARRIED: dict[type, tuple[str, ...]] = {
+    GELU: ("approximate",), Dropout: ("p",), LeakyReLU: ("negative_slope",), Hardtanh: ("min_val", "max_val"),
+    ELU: ("alpha",), CELU: ("alpha",), Softplus: ("beta", "threshold"),
+}
 
-    target = REPLACEMENTS.get(type(module))
-    if target is None:
+
+def replace(module: nn.Module) -> nn.Module | None:
+    """The packed twin of ``module`` carrying its hyper-parameters, or ``None`` when the
+    module has no twin."""
+
+    twin = REPLACEMENTS.get(type(module))
+    if twin is None:
         return None
-    if target is GELU:
-        return GELU(getattr(module, "approximate", "none"))
-    if target is Dropout:
-        return Dropout(getattr(module, "p", 0.5))
-    if target is LeakyReLU:
-        return LeakyReLU(getattr(module, "negative_slope", 0.01))
-    if target is Hardtanh:
-        return Hardtanh(getattr(module, "min_val", -1.0), getattr(module, "max_val", 1.0))
-    if target in (ELU, CELU):
-        return target(getattr(module, "alpha", 1.0))
-    if target is Softplus:
-        return Softplus(getattr(module, "beta", 1.0), getattr(module, "threshold", 20.0))
-    return target()
+    carried = {name: getattr(module, name) for name in _CARRIED.get(twin, ()) if hasattr(module, name)}
+    return twin(**carried)
 
 
 # -- functional call sites ----------------------------------------------------------
@@ -650,17 +668,20 @@ _PATCHES = (
 
 @contextmanager
 def packed_activations():
-    """Inside the context, ``F.relu`` / ``F.gelu`` / ... called directly on the output
-    of a converted layer use the packed versions; every other call is untouched.
-    The patch is undone on exit, also on an exception."""
+    """Inside the context, ``F.relu`` / ``F.gelu`` / ... called directly on the output of a
+    converted layer use the packed versions; every other call is untouched.  Whatever was
+    patched is put back on exit -- in reverse order, and also when the body or the patching
+    itself raises."""
 
-    saved = [(owner, name, getattr(owner, name)) for owner, name, _ in _PATCHES]
-    for owner, name, replacement in _PATCHES:
-        setattr(owner, name, replacement)
+    undo: list[tuple[object, str, object]] = []
     try:
+        for owner, name, replacement in _PATCHES:
+            undo.append((owner, name, getattr(owner, name)))
+            setattr(owner, name, replacement)
         yield
     finally:
-        for owner, name, original in saved:
+        while undo:
+            owner, name, original = undo.pop()
             setattr(owner, name, original)
 
 

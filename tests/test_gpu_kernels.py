@@ -106,6 +106,23 @@ def test_pack_affine_rows_is_bit_exact_for_every_dtype_and_ragged_width(rows, co
     assert np.array_equal(host(scale), want_scale)
 
 
+@pytest.mark.parametrize("rows,columns", [(1, 64), (33, 2048), (257, 4096), (64, 128), (7, 14336), (5, 72), (3, 64 + 8)])
+def test_pack_coordinate_and_pack_bits_at_layer_widths_equal_the_oracle(rows, columns):
+    """Widths that are multiples of 64 take the 64-bytes-per-thread kernel; the others the
+    byte-per-thread one (cpu.cpp:207-277 of the reference)."""
+
+    generator = torch.Generator().manual_seed(rows + columns)
+    coordinate = torch.randint(-127, 128, (rows, columns), generator=generator, dtype=torch.int32).to(torch.int8)
+    coordinate[0, : min(columns, 9)] = 0  # zero counts as +1
+    assert np.array_equal(host(kernels.pack_coordinate(coordinate.to(DEVICE))), oracle.pack_coordinate(coordinate))
+    mask = torch.rand(rows, columns, generator=generator) < 0.3
+    assert np.array_equal(host(kernels.pack_bits(mask.to(DEVICE))), oracle.pack_bits(mask))
+    # a view that does not start on a 16-byte boundary falls back to the narrow kernel
+    shifted = torch.zeros(rows * columns + 1, dtype=torch.int8, device=DEVICE)[1:].view(rows, columns)
+    shifted.copy_(coordinate)
+    assert np.array_equal(host(kernels.pack_coordinate(shifted)), oracle.pack_coordinate(coordinate))
+
+
 def test_pack_handles_empty_and_constant_rows():
     bits, offset, scale = kernels.pack_affine_rows(torch.zeros(0, 16, device=DEVICE))
     assert bits.shape == (0, 2) and offset.numel() == 0
