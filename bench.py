@@ -355,7 +355,8 @@ def kernel_roofline(device, tokens: int, dim: int = D_MODEL, ffn: int = D_FFN) -
             # 151.4 MB read + 449.7 MB written; algorithmic 611 MB, the last tiles of Y were still in
             # L2).  Other token counts: activations in and out scale with the tokens, the bits do not.
             "traffic": ((601.1e6 - 7.3e6) * m / 16384 + 7.3e6) if (k, n) == (D_MODEL, D_FFN) else None,
-            "traffic_source": "ncu capture of one launch at 16384 tokens" + ("" if m == 16384 else ", scaled by the token count"),
+            "traffic_source": None if (k, n) != (D_MODEL, D_FFN) else
+            "ncu capture of one launch at 16384 tokens" + ("" if m == 16384 else ", scaled by the token count"),
             "algorithmic_bytes": m * k * 2 + n * k / 8 + 4 * n + m * n * 2,
             "us_per_launch": seconds * 1e6}
 

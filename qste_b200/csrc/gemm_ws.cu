@@ -23,6 +23,12 @@
 //   warps 16-19 epilogue: tcgen05.ld, fp32 scale and bias per weight row, transposed store
 //   warp 20     TMA producer of the X tiles (one lane; no multicast)
 //   warp 21     MMA issuer (one lane): four K = 16 MMAs per k-block, tcgen05.commit
+//   warp 22     TMA producer of the sign bits (one lane): chunks of slab rows x 64 bytes (eight
+//               k-blocks) into a shared-memory ring, four chunks deep.  The expanders read their
+//               8 bytes per k-block from there: with the bits loaded straight from global memory
+//               into registers, every expander iteration ended on a ~1.4 us round trip to DRAM
+//               (a row per lane, one sector each) and the kernel ran at 0.36 us per k-block
+//               whatever the batch -- 27 us at K = 4096 against 7 us of work.
 //
 // A build switch keeps the expanded operand in shared memory instead (kATmem = false: the
 // layout and descriptors of the large-batch kernel), as a cross-check of the tensor-memory path.
@@ -44,8 +50,12 @@ constexpr int kBK = 64;          // k-values per stage
 constexpr int kGroups = 4, kGroupWarps = 4;
 constexpr int kExpanderWarps = kGroups * kGroupWarps;
 constexpr int kEpilogueWarps = 4;
-constexpr int kTmaWarp = kExpanderWarps + kEpilogueWarps, kMmaWarp = kTmaWarp + 1;
-constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kTmaWarp = kExpanderWarps + kEpilogueWarps, kMmaWarp = kTmaWarp + 1, kBitsWarp = kMmaWarp + 1;
+constexpr int kThreads = (kBitsWarp + 1) * 32;
+constexpr int kChunkBlocks = 8;                      // k-blocks per chunk of sign bits
+constexpr int kChunkRowBytes = kChunkBlocks * 8;     // 64 bytes of a weight row
+constexpr int kBitStages = 4;
+constexpr uint32_t kBitStageBytes = kSlabRows * kChunkRowBytes;
 constexpr int kMaxTokens = 128;
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kAccumColumns = 128;     // columns per accumulator (two of them)
@@ -57,7 +67,8 @@ template <bool kATmem> struct WsShape {
   static constexpr uint32_t kABytes = kATmem ? 0u : (uint32_t)(kSlabRows * kBK * 2);
   static constexpr uint32_t kXBytes = kMaxTokens * kBK * 2;   // room for the largest X tile
   static constexpr uint32_t kStageBytes = kABytes + kXBytes;
-  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kBitStages * kBitStageBytes + 1024 /*alignment slack*/ +
+                                         256 /*barriers*/;
 };
 
 struct WsParams {
@@ -73,6 +84,7 @@ struct WsParams {
   int kblocks;
   int is_half;             // X (and the expanded weights) are fp16, else bf16
   unsigned long long* diagnostics;
+  int profile;             // CTA 0 leaves per-role cycle counts in diagnostics[8..23]
 };
 
 __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
@@ -111,7 +123,8 @@ __device__ __forceinline__ void tmem_load16(uint32_t address, float* v) {
 
 template <typename TO, bool kATmem>
 __global__ void __launch_bounds__(kThreads, 1)
-packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ WsParams p) {
+packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_bits,
+                      const __grid_constant__ WsParams p) {
   using Shape = WsShape<kATmem>;
   constexpr int kStages = Shape::kStages;
   constexpr uint32_t kStageBytes = Shape::kStageBytes;
@@ -119,20 +132,25 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  // stage s: [expanded A tile (shared-memory variant only)] [X tile]
-  const uint32_t bar_base = smem_base + kStages * kStageBytes;
+  // stage s: [expanded A tile (shared-memory variant only)] [X tile]; then the ring of bit chunks
+  const uint32_t bits_base = smem_base + kStages * kStageBytes;
+  const uint32_t bar_base = bits_base + kBitStages * kBitStageBytes;
   // full(s): the TMA thread (with the X bytes) plus one arrival per warp of the group that wrote
   // the A tile; empty(s): one arrival, from tcgen05.commit
   auto full = [&](int s) { return bar_base + 8u * s; };
   auto empty = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto accum_full = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto accum_empty = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_aligned + (bar_base - smem_base) + 8 * (2 * kStages + 4));
+  // bits_full(b): the bits producer (with the chunk's bytes); bits_empty(b): every expander warp
+  auto bits_full = [&](int b) { return bar_base + 8u * (2 * kStages + 4 + b); };
+  auto bits_empty = [&](int b) { return bar_base + 8u * (2 * kStages + 4 + kBitStages + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_aligned + (bar_base - smem_base) + 8 * (2 * kStages + 4 + 2 * kBitStages));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int np = p.tokens_padded;
   const uint32_t x_bytes = (uint32_t)np * kBK * 2;
+  const int chunks = (p.kblocks + kChunkBlocks - 1) / kChunkBlocks;   // per slab
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -142,6 +160,10 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     for (int a = 0; a < 2; ++a) {
       mbar_init(accum_full(a), 1);
       mbar_init(accum_empty(a), kEpilogueWarps);
+    }
+    for (int b = 0; b < kBitStages; ++b) {
+      mbar_init(bits_full(b), 1);
+      mbar_init(bits_empty(b), kExpanderWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -167,6 +189,23 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       }
     }
     __syncwarp();
+  } else if (warp == kBitsWarp) {
+    // ---- sign bits: slab rows x 64 bytes per chunk (the box is slab_rows tall; bytes past K/8
+    // and rows past N read zero) ---------------------------------------------------------------
+    if (lane == 0) {
+      int h = 0;
+      bool alive = true;
+      const uint32_t chunk_bytes = (uint32_t)p.slab_rows * kChunkRowBytes;
+      for (int slab = blockIdx.x; slab < p.slabs && alive; slab += gridDim.x) {
+        for (int c = 0; c < chunks; ++c, ++h) {
+          const int b = h % kBitStages;
+          if (!WAIT(bits_empty(b), ((h / kBitStages) & 1) ^ 1)) { alive = false; break; }
+          mbar_expect_tx(bits_full(b), chunk_bytes);
+          tma_load_2d(bits_base + b * kBitStageBytes, &map_bits, bits_full(b), c * kChunkRowBytes, slab * p.slab_rows);
+        }
+      }
+    }
+    __syncwarp();
   } else if (warp == kMmaWarp) {
     // ---- MMA issuer -------------------------------------------------------------------------
     if (lane == 0) {
@@ -176,6 +215,8 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                              ((uint32_t)(np >> 3) << 17) | ((uint32_t)(kSlabRows >> 4) << 24);
       int g = 0, lt = 0;
       bool alive = true;
+      const bool prof = p.profile && blockIdx.x == 0 && p.diagnostics;
+      long long t_begin = prof ? clock64() : 0, t_wait = 0, t_issue = 0, t_mark = 0;
       for (int slab = blockIdx.x; slab < p.slabs && alive; slab += gridDim.x, ++lt) {
         const int acc = lt & 1;
         if (!WAIT(accum_empty(acc), ((lt >> 1) & 1) ^ 1)) break;
@@ -183,7 +224,9 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * kAccumColumns;
         for (int kb = 0; kb < p.kblocks; ++kb, ++g) {
           const int s = g % kStages;
+          if (prof) t_mark = clock64();
           if (!WAIT(full(s), (g / kStages) & 1)) { alive = false; break; }
+          if (prof) { const long long now = clock64(); t_wait += now - t_mark; t_mark = now; }
           tc_fence_after();
           const uint32_t stage = smem_base + s * kStageBytes;
           const uint32_t x_smem = stage + Shape::kABytes;
@@ -191,17 +234,25 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           for (int ks = 0; ks < kBK / 16; ++ks) {
             // K-major, 128-byte swizzle: rows of 64 values = 128 B, 8-row groups 1024 B apart
             const uint64_t desc_x = make_desc(x_smem + ks * 32, 16, 1024);
+            const uint32_t d = tmem_d;
+            const uint32_t accumulate = (kb | ks) != 0 ? 1u : 0u;
             if (kATmem) {
               // 16 k-values of a lane are 8 columns of 32 bits
-              umma_ts(tmem_d, tmem_base + kAColumn0 + (uint32_t)s * kAStageColumns + (uint32_t)ks * 8u, desc_x, idesc,
-                      (kb | ks) != 0 ? 1u : 0u);
+              umma_ts(d, tmem_base + kAColumn0 + (uint32_t)s * kAStageColumns + (uint32_t)ks * 8u, desc_x, idesc, accumulate);
             } else {
-              umma(tmem_d, make_desc(stage + ks * 32, 16, 1024), desc_x, idesc, (kb | ks) != 0 ? 1u : 0u);
+              umma(d, make_desc(stage + ks * 32, 16, 1024), desc_x, idesc, accumulate);
             }
           }
           umma_commit(empty(s));
+          if (prof) t_issue += clock64() - t_mark;
         }
         if (alive) umma_commit(accum_full(acc));
+      }
+      if (prof) {
+        p.diagnostics[8] = (unsigned long long)(clock64() - t_begin);  // MMA thread: whole loop
+        p.diagnostics[9] = (unsigned long long)t_wait;                 //   waiting for a full stage
+        p.diagnostics[10] = (unsigned long long)t_issue;               //   fence + 4 MMAs + commit
+        p.diagnostics[11] = (unsigned long long)g;                     //   k-blocks
       }
     }
     __syncwarp();
@@ -216,32 +267,49 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int swizzle = row_in_slab & 7;
     bool alive = true;
     int first = 0;  // k-blocks of the slabs before the current one
+    int h = 0;      // chunks of bits before the current one
+    // this thread's 8 bytes per k-block sit at row * 64 + (k-block % 8) * 8 of a chunk; rows past
+    // the slab read whatever the ring holds there: they are computed and never stored
+    const uint32_t my_bits = bits_base + (uint32_t)(row_in_slab < p.slab_rows ? row_in_slab : 0) * kChunkRowBytes;
+    const bool prof = p.profile && blockIdx.x == 0 && p.diagnostics && threadIdx.x == 0;
+    long long t_begin = prof ? clock64() : 0, t_bits = 0, t_empty = 0, t_store = 0, t_mark = 0;
     for (int slab = blockIdx.x; slab < p.slabs && alive; slab += gridDim.x) {
-      long long row = (long long)slab * p.slab_rows + (row_in_slab < p.slab_rows ? row_in_slab : 0);
-      if (row >= p.N) row = p.N - 1;   // rows past the slab or past N are computed and never stored
-      const uint8_t* source = p.bits + row * p.bit_pitch;
-      auto fetch = [&](int kb) {
-        return *reinterpret_cast<const unsigned long long*>(source + (long long)(kb < p.kblocks ? kb : p.kblocks - 1) * 8);
-      };
-      // this group's k-blocks of the slab are kb = group, group + 4, ...; two loads stay in flight
-      unsigned long long word = fetch(group), next_word = fetch(group + kGroups);
-      for (int kb = group; kb < p.kblocks && alive; kb += kGroups) {
-        const unsigned long long after_next = fetch(kb + 2 * kGroups);
-        const int n = first + kb;
-        const int s = n % kStages;
-        // warp-uniform: the tensor-memory store below is a warp-wide instruction
-        alive = __all_sync(0xffffffffu, WAIT(empty(s), ((n / kStages) & 1) ^ 1));
-        if (alive) {
-          const uint32_t lo = (uint32_t)word, hi = (uint32_t)(word >> 32);
+      for (int c = 0; c < chunks && alive; ++c, ++h) {
+        const int b = h % kBitStages;
+        if (prof) t_mark = clock64();
+        alive = __all_sync(0xffffffffu, WAIT(bits_full(b), (h / kBitStages) & 1));
+        if (prof) t_bits += clock64() - t_mark;
+        if (!alive) break;
+        // both of this group's k-blocks of the chunk (kb = 8c + group and 8c + group + 4) are read
+        // now, so the slot can go back to the producer before the expansion starts
+        uint32_t words[2][2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(words[i][0]), "=r"(words[i][1])
+                       : "r"(my_bits + b * kBitStageBytes + (uint32_t)(group + kGroups * i) * 8u) : "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bits_empty(b));
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int kb = c * kChunkBlocks + group + kGroups * i;
+          if (kb >= p.kblocks) break;
+          const int n = first + kb;
+          const int s = n % kStages;
+          // warp-uniform: the tensor-memory store below is a warp-wide instruction
+          if (prof) t_mark = clock64();
+          alive = __all_sync(0xffffffffu, WAIT(empty(s), ((n / kStages) & 1) ^ 1));
+          if (prof) { const long long now = clock64(); t_empty += now - t_mark; t_mark = now; }
+          if (!alive) break;
+          const uint32_t lo = words[i][0], hi = words[i][1];
           if (kATmem) {
             tc_fence_after();
             uint32_t r[32];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const uint4 a = expand_byte((lo >> (8 * e)) & 0xffu, minus_one);
-              const uint4 b = expand_byte((hi >> (8 * e)) & 0xffu, minus_one);
-              r[4 * e] = a.x; r[4 * e + 1] = a.y; r[4 * e + 2] = a.z; r[4 * e + 3] = a.w;
-              r[16 + 4 * e] = b.x; r[16 + 4 * e + 1] = b.y; r[16 + 4 * e + 2] = b.z; r[16 + 4 * e + 3] = b.w;
+              const uint4 lower = expand_byte((lo >> (8 * e)) & 0xffu, minus_one);
+              const uint4 upper = expand_byte((hi >> (8 * e)) & 0xffu, minus_one);
+              r[4 * e] = lower.x; r[4 * e + 1] = lower.y; r[4 * e + 2] = lower.z; r[4 * e + 3] = lower.w;
+              r[16 + 4 * e] = upper.x; r[16 + 4 * e + 1] = upper.y; r[16 + 4 * e + 2] = upper.z; r[16 + 4 * e + 3] = upper.w;
             }
             tmem_store32(lane_address + (uint32_t)s * kAStageColumns, r);
             tc_fence_before();
@@ -254,13 +322,18 @@ packed_gemm_ws_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             fence_proxy_async();
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full(s));
+          if (prof) t_store += clock64() - t_mark;
         }
-        __syncwarp();
-        if (lane == 0 && alive) mbar_arrive(full(s));
-        word = next_word;
-        next_word = after_next;
       }
       first += p.kblocks;
+    }
+    if (prof) {
+      p.diagnostics[12] = (unsigned long long)(clock64() - t_begin);  // expander warp 0: whole loop
+      p.diagnostics[13] = (unsigned long long)t_bits;                 //   waiting for a chunk of bits
+      p.diagnostics[14] = (unsigned long long)t_empty;                //   waiting for a free stage
+      p.diagnostics[15] = (unsigned long long)t_store;                //   expand + store + arrive
     }
   } else {
     // ---- epilogue: D^T[weight row, token] -> Y[token, weight row] ----------------------------
@@ -326,7 +399,7 @@ int ws_variant() {
 }
 
 template <typename TO, bool kATmem>
-int launch_ws(const CUtensorMap& map, const WsParams& params, int grid, cudaStream_t stream) {
+int launch_ws(const CUtensorMap& map, const CUtensorMap& map_bits, const WsParams& params, int grid, cudaStream_t stream) {
   auto kernel = packed_gemm_ws_kernel<TO, kATmem>;
   static bool configured[64] = {};
   int device = 0;
@@ -340,7 +413,7 @@ int launch_ws(const CUtensorMap& map, const WsParams& params, int grid, cudaStre
     }
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  kernel<<<(unsigned)grid, kThreads, WsShape<kATmem>::kSmemBytes, stream>>>(map, params);
+  kernel<<<(unsigned)grid, kThreads, WsShape<kATmem>::kSmemBytes, stream>>>(map, map_bits, params);
   note_launches(1);
   return launch_status("packed_gemm_ws");
 }
@@ -352,15 +425,15 @@ bool ws_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, con
   if (samples < 1 || samples > kMaxTokens || rows < 1 || columns < kBK) return false;
   if (dtype != QSTE_BF16 && dtype != QSTE_F16) return false;   // fp32 inputs take the three-plane kernel
   if (out_dtype != dtype) return false;
-  if (columns % kBK != 0) return false;                          // whole 8-byte groups of bits per k-block
-  if (!aligned(x, 16) || !aligned(bits, 8) || !aligned(out, 2)) return false;
+  if (columns % 128 != 0) return false;   // whole k-blocks, and bit rows that start on 16-byte boundaries (TMA)
+  if (!aligned(x, 16) || !aligned(bits, 16) || !aligned(out, 2)) return false;
   if (rows > (1ll << 30) || columns > (1ll << 30)) return false;
   return check_arch() == QSTE_OK;
 }
 
 // Slabs of weight rows: 128-row slabs when those already give every SM one, else
 // ceil(N / SMs) rows each, so that one wave covers the matrix (97 rows at N = 14336 on 148 SMs).
-static void ws_slabs(int64_t rows, int* slab_rows, int* slabs) {
+void ws_slabs(int64_t rows, int* slab_rows, int* slabs) {
   const int sms = sm_count();
   long long count = ceil_div(rows, kSlabRows);
   if (count < sms) count = rows < sms ? rows : sms;
@@ -368,18 +441,15 @@ static void ws_slabs(int64_t rows, int* slab_rows, int* slabs) {
   *slabs = (int)ceil_div(rows, *slab_rows);
 }
 
-// Whether the weight-stationary kernel is expected to beat the large-batch one: always for a
-// handful of tokens; with more tokens only while the unused rows of thin slabs (few output rows
-// spread over all SMs, each walking the whole contraction) do not cost more tensor time than
-// the large-batch kernel's 256-column tiles.
+// Where the weight-stationary kernel beats the others (graph-replay times over rotating weight
+// copies, bf16): its cost is the number of MMAs a CTA issues -- about 160 cycles each at M = 128,
+// K = 16, whatever the token count -- so it wins where a slab's contraction is short and the
+// matrix is wide enough to give every SM a slab: 4096 -> 14336 takes 25.6-32.3 us for 1..128 tokens
+// against 28.9-36.8 us on the 256-column tiles of the large-batch kernel (and 38.4 us for the
+// four-token table kernel), while 14336 -> 4096 takes 76 us against 27.
 bool ws_preferred(int64_t samples, int64_t rows, int64_t columns) {
-  int slab_rows, slabs;
-  ws_slabs(rows, &slab_rows, &slabs);
-  const long long waves = ceil_div(slabs, sm_count());
-  const long long np = ceil_div(samples, 16) * 16;
-  // cycles per k-block: the MMAs (128 x Np x 64 at ~4000 FMA per cycle) or the fixed cost of a stage
-  const long long per_kblock = 2 * np > 80 ? 2 * np : 80;
-  return waves * (columns / kBK) * per_kblock < 36000;  // ~19 us
+  if (columns > 4096) return false;
+  return samples <= 4 ? rows >= 8192 : rows >= 12288;
 }
 
 int ws_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale, const float* bias,
@@ -400,6 +470,10 @@ int ws_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed,
   params.kblocks = (int)(columns / kBK);
   params.is_half = dtype == QSTE_F16 ? 1 : 0;
   params.diagnostics = diagnostics;
+  {
+    static const int profile = getenv("QSTE_B200_WS_PROFILE") ? atoi(getenv("QSTE_B200_WS_PROFILE")) : 0;
+    params.profile = profile;
+  }
 
   // X as a [M, K] row-major 16-bit matrix; boxes of 64 k-values x Np rows (rows past M read 0)
   CUtensorMap map;
@@ -415,12 +489,26 @@ int ws_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed,
     set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(ws)");
     return QSTE_ERR_CUDA;
   }
+  // the sign bits as a [N, K/8] byte matrix; boxes of 64 bytes (eight k-blocks) x slab_rows rows
+  CUtensorMap map_bits;
+  cuuint64_t bit_dims[2] = {(cuuint64_t)params.bit_pitch, (cuuint64_t)rows};
+  cuuint64_t bit_strides[1] = {(cuuint64_t)params.bit_pitch};
+  cuuint32_t bit_box[2] = {(cuuint32_t)kChunkRowBytes, (cuuint32_t)params.slab_rows};
+  const CUresult bit_result = encode(&map_bits, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(packed), bit_dims,
+                                     bit_strides, bit_box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (bit_result != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(ws bits)");
+    return QSTE_ERR_CUDA;
+  }
   const int grid = params.slabs < sms ? params.slabs : sms;
   const bool a_in_tmem = ws_variant() == 0;
   if (out_dtype == QSTE_F16)
-    return a_in_tmem ? launch_ws<__half, true>(map, params, grid, stream) : launch_ws<__half, false>(map, params, grid, stream);
-  return a_in_tmem ? launch_ws<__nv_bfloat16, true>(map, params, grid, stream)
-                   : launch_ws<__nv_bfloat16, false>(map, params, grid, stream);
+    return a_in_tmem ? launch_ws<__half, true>(map, map_bits, params, grid, stream)
+                     : launch_ws<__half, false>(map, map_bits, params, grid, stream);
+  return a_in_tmem ? launch_ws<__nv_bfloat16, true>(map, map_bits, params, grid, stream)
+                   : launch_ws<__nv_bfloat16, false>(map, map_bits, params, grid, stream);
 }
 
 }  // namespace qste

@@ -44,10 +44,19 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
   cudaStream_t s = as_stream(stream);
   const int64_t pitch = (columns + 7) / 8;
 
-  if (path == QSTE_PATH_SMALL ||
-      (path == QSTE_PATH_AUTO && small_batch_auto() && ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype) &&
-       ws_preferred(samples, rows, columns))) {
-    if (!ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype)) return QSTE_ERR_UNSUPPORTED;
+  // Small batches (all measured as CUDA-graph replays over rotating weight copies):
+  //   1-2 tokens   the look-up-table kernel (gemm_lut.cu): bits streamed once, a thread per weight row
+  //   3-4 tokens   the weight-stationary tcgen05 kernel (gemm_ws.cu) on wide, short matrices, else the
+  //                table kernel
+  //   5-128        the weight-stationary kernel where it wins (ws_preferred), else the large-batch tiles
+  const bool small_auto = path == QSTE_PATH_AUTO && small_batch_auto();
+  const bool ws_fits = ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype);
+  const bool ws_wins = small_auto && ws_fits && samples >= 3 && ws_preferred(samples, rows, columns);
+  if ((path == QSTE_PATH_STREAM || (small_auto && !ws_wins)) &&
+      lut_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype))
+    return lut_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, s);
+  if (path == QSTE_PATH_SMALL || ws_wins) {
+    if (!ws_fits) return QSTE_ERR_UNSUPPORTED;
     if (!workspace || workspace_bytes < kHeader) return QSTE_ERR_WORKSPACE;
     return ws_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, out_dtype,
                       static_cast<unsigned long long*>(workspace), s);

@@ -42,7 +42,9 @@ def pack_affine_rows(values):
 
 
 def pack_coordinate(coordinate):
-    return _t(oracle.pack_coordinate(coordinate))
+    # Surface.__init__ sends a host matrix through the current CUDA device when there is one
+    # (the product has no CPU kernel); under this backend that tensor comes back to the host
+    return _t(oracle.pack_coordinate(coordinate.cpu())).to(coordinate.device)
 
 
 def packed_linear_affine(inputs, packed, scale, bias, columns):
