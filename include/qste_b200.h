@@ -56,8 +56,7 @@ typedef enum {
   QSTE_PATH_AUTO = 0,   /* tcgen05 tensor-core kernel when the shape allows it, else the others */
   QSTE_PATH_SIMT = 1,   /* generic CUDA-core kernel (any shape) */
   QSTE_PATH_TENSOR = 2, /* tcgen05/TMEM kernel; QSTE_ERR_UNSUPPORTED when the shape does not fit */
-  QSTE_PATH_STREAM = 3, /* packed-bit streaming kernel on the CUDA cores, batches of 1-4 (forward only) */
-  QSTE_PATH_SMALL = 4   /* weight-stationary tcgen05 kernel, batches of 1-128, bf16/fp16 (forward only) */
+  QSTE_PATH_STREAM = 3  /* packed-bit streaming kernels on the CUDA cores, batches of 1-4 (forward only) */
 } qste_path;
 
 int qste_b200_abi_version(void);

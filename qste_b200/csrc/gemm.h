@@ -47,15 +47,7 @@ bool tc_supported(int kind, int64_t I, int64_t J, int64_t K, int dtype, const vo
                   const void* bits, const void* out, int out_dtype);
 int tc_run(const TcProblem& problem, cudaStream_t stream);
 
-// Small-batch forward, weight-stationary (gemm_ws.cu): 1..128 tokens of bf16 / fp16.
-bool ws_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x,
-                  const void* bits, const void* out, int out_dtype);
-bool ws_preferred(int64_t samples, int64_t rows, int64_t columns);
-int ws_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,
-               const float* bias, int64_t rows, int64_t columns, void* out, int out_dtype,
-               unsigned long long* diagnostics, cudaStream_t stream);
-
-// Forward for 1..8 tokens on the CUDA cores, bound by streaming the bits (gemm_lut.cu).
+// Forward for 1..4 tokens on the CUDA cores, bound by streaming the bits (gemm_lut.cu).
 bool lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x,
                    const void* bits, const void* out, int out_dtype);
 int lut_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,

@@ -481,6 +481,125 @@ coordinate_and_pack_fast_kernel(const float* __restrict__ moment, int8_t* __rest
     atomicAdd(reinterpret_cast<unsigned long long*>(&scalars->flips), (unsigned long long)local_flips);
 }
 
+// The same step when the moment pass did NOT write the moments back (moment_vec_kernel<true,
+// false>): `evidence` still holds the reduced evidence, and the moment of an element is formed
+// again here, operation for operation as the moment pass formed it --
+//     u = (g * row_factor) * column_factor,   m = moment_q * (old_scale * beta1) + u * gain
+// -- so the bits are the same and the matrix of fp32 moments (4 bytes per coordinate written by
+// one kernel and read by the next) never exists.  `new_scale` holds the block scales the moment
+// pass derived; `moment_scale` still holds the old ones and is overwritten afterwards
+// (commit_scales_kernel).  Needs C % 8 == 0 and a power-of-two block of at least 8.
+struct LeanInputs {
+  float4 lo, hi, factor_lo, factor_hi;
+  uint2 coordinate, moment;
+  float row_factor;
+  unsigned short old_scale, new_scale;
+  uint8_t bits;
+};
+
+__global__ void __launch_bounds__(256)
+coordinate_and_pack_lean_kernel(const float* __restrict__ evidence, int8_t* __restrict__ coordinate,
+                                uint8_t* __restrict__ packed, int8_t* __restrict__ moment_q,
+                                const uint16_t* __restrict__ moment_scale, const uint16_t* __restrict__ new_scale,
+                                const float* __restrict__ row_factor, const float* __restrict__ column_factor,
+                                int64_t total, int64_t C8, int block_shift, float beta1, uint32_t seed_hash,
+                                int64_t step_host, const int64_t* __restrict__ step_device, UpdateScalars* scalars,
+                                const uint8_t* update_enabled) {
+  if (disabled(update_enabled)) return;
+  const int64_t step = step_device ? *step_device : step_host;
+  const uint32_t hash_seed = seed_hash ^ scramble((uint32_t)step ^ 0x2545f491u);
+  const float coordinate_step = scalars->coordinate_step;
+  const float gain = scalars->gain;
+  constexpr float kMagic = 12582912.0f;
+  constexpr int kMagicBits = 0x4b400000;
+  auto load = [&](int64_t q, int64_t row, int64_t column8) {
+    LeanInputs in;
+    const int64_t base = q * 8;
+    in.lo = *reinterpret_cast<const float4*>(evidence + base);
+    in.hi = *reinterpret_cast<const float4*>(evidence + base + 4);
+    in.factor_lo = *reinterpret_cast<const float4*>(column_factor + column8 * 8);
+    in.factor_hi = *reinterpret_cast<const float4*>(column_factor + column8 * 8 + 4);
+    in.row_factor = row_factor[row];
+    in.coordinate = *reinterpret_cast<const uint2*>(coordinate + base);
+    in.moment = *reinterpret_cast<const uint2*>(moment_q + base);
+    in.old_scale = moment_scale[base >> block_shift];
+    in.new_scale = new_scale[base >> block_shift];
+    in.bits = packed[q];
+    return in;
+  };
+  int local_flips = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t stride_rows = stride / C8, stride_columns = stride - stride_rows * C8;
+  int64_t q = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  int64_t row = q / C8, column8 = q - row * C8;
+  LeanInputs current = {}, following = {};
+  if (q < total) current = load(q, row, column8);
+  while (q < total) {
+    const int64_t next_q = q + stride;
+    row += stride_rows;
+    column8 += stride_columns;
+    if (column8 >= C8) { column8 -= C8; ++row; }
+    if (next_q < total) following = load(next_q, row, column8);
+    const int64_t base = q * 8;
+    const float g[8] = {current.lo.x, current.lo.y, current.lo.z, current.lo.w,
+                        current.hi.x, current.hi.y, current.hi.z, current.hi.w};  // constant indices below
+    const float cf[8] = {current.factor_lo.x, current.factor_lo.y, current.factor_lo.z, current.factor_lo.w,
+                         current.factor_hi.x, current.factor_hi.y, current.factor_hi.z, current.factor_hi.w};
+    const uint2 old_c = current.coordinate, old_m = current.moment;
+    const float decay = __half2float(__ushort_as_half(current.old_scale)) * beta1;
+    const float inverse_scale = 1.0f / fmaxf(__half2float(__ushort_as_half(current.new_scale)), 1e-12f);
+    const float rf = current.row_factor;
+    const uint32_t index = (uint32_t)base;
+    unsigned next = 0;
+    uint32_t c_lo = 0u, c_hi = 0u, m_lo = 0u, m_hi = 0u;  // scalars: arrays here end up in local memory
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int old_value = (int)(int8_t)(((e < 4 ? old_c.x : old_c.y) >> (8 * (e & 3))) & 0xffu);
+      const int old_moment = (int)(int8_t)(((e < 4 ? old_m.x : old_m.y) >> (8 * (e & 3))) & 0xffu);
+      const float update = g[e] * rf * cf[e];
+      const float m = (float)old_moment * decay + update * gain;
+      const float old_float = __int_as_float(kMagicBits + old_value) - kMagic;
+      const float target = old_float - m * coordinate_step;
+      float lower;
+      if (fabsf(target) < 4194304.0f) {
+        const float nearest = (target + kMagic) - kMagic;
+        lower = nearest - (nearest > target ? 1.0f : 0.0f);
+      } else {
+        lower = floorf(target);
+      }
+      const float uniform = __uint2float_rn(scramble((index + e) ^ hash_seed)) * (1.0f / 4294967296.0f);
+      const float rounded = lower + (uniform < (target - lower) ? 1.0f : 0.0f);
+      const int new_c = __float_as_int(fminf(127.0f, fmaxf(-127.0f, rounded)) + kMagic) - kMagicBits;
+      const float scaled = fminf(127.0f, fmaxf(-127.0f, m * inverse_scale));
+      const int new_m = __float_as_int(scaled + kMagic) - kMagicBits;
+      if (new_c >= 0) next |= 1u << e;
+      const uint32_t c_byte = ((uint32_t)new_c & 0xffu) << (8 * (e & 3));
+      const uint32_t m_byte = ((uint32_t)new_m & 0xffu) << (8 * (e & 3));
+      if (e < 4) { c_lo |= c_byte; m_lo |= m_byte; } else { c_hi |= c_byte; m_hi |= m_byte; }
+    }
+    *reinterpret_cast<uint2*>(coordinate + base) = make_uint2(c_lo, c_hi);
+    *reinterpret_cast<uint2*>(moment_q + base) = make_uint2(m_lo, m_hi);
+    local_flips += __popc((unsigned)current.bits ^ next);
+    packed[q] = (uint8_t)next;
+    current = following;
+    q = next_q;
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1)
+    local_flips += __shfl_xor_sync(0xffffffffu, local_flips, offset);
+  if ((threadIdx.x & 31) == 0 && local_flips)
+    atomicAdd(reinterpret_cast<unsigned long long*>(&scalars->flips), (unsigned long long)local_flips);
+}
+
+// the block scales of this step take the place of the old ones once every element has used both
+__global__ void __launch_bounds__(256)
+commit_scales_kernel(const uint16_t* __restrict__ new_scale, uint16_t* __restrict__ moment_scale, int64_t blocks,
+                     const uint8_t* update_enabled) {
+  if (disabled(update_enabled)) return;
+  for (int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; b < blocks; b += (int64_t)gridDim.x * blockDim.x)
+    moment_scale[b] = new_scale[b];
+}
+
 __global__ void __launch_bounds__(256)
 coordinate_and_pack_kernel(const float* __restrict__ moment, int8_t* __restrict__ coordinate,
                            uint8_t* __restrict__ packed, int8_t* __restrict__ moment_q,
@@ -849,10 +968,13 @@ precondition_quad_kernel(const float* __restrict__ g, int64_t R, int64_t C, cons
 // kRecompute = true: g still holds the evidence; the normalised update (g * row_factor) *
 // column_factor is formed here, exactly as precondition_vec_kernel forms it (needs C % 4 == 0,
 // so that four consecutive elements share a row).
-template <bool kRecompute>
+// kWriteBack = false (only with kRecompute): the moments are not stored -- the last pass forms them
+// again from the evidence (coordinate_and_pack_lean_kernel) -- and the new block scales go to
+// `scale_out` instead of replacing the old ones, which that pass still needs.
+template <bool kRecompute, bool kWriteBack>
 __global__ void __launch_bounds__(32)
 moment_vec_kernel(float* __restrict__ g, const int8_t* __restrict__ moment_q,
-                  uint16_t* __restrict__ moment_scale, int64_t count, int64_t block_size, int64_t blocks,
+                  uint16_t* __restrict__ moment_scale, uint16_t* __restrict__ scale_out, int64_t count, int64_t block_size, int64_t blocks,
                   float beta1, const UpdateScalars* __restrict__ scalars,
                   double* __restrict__ block_partial, const uint8_t* update_enabled, int64_t C,
                   const float* __restrict__ row_factor, const float* __restrict__ column_factor) {
@@ -940,11 +1062,13 @@ moment_vec_kernel(float* __restrict__ g, const int8_t* __restrict__ moment_q,
           maximum = fmaxf(maximum, fabsf(moment));
         }
       }
-      *cell = make_float4(values[0], values[1], values[2], values[3]);
+      if (kWriteBack) *cell = make_float4(values[0], values[1], values[2], values[3]);
     }
     __syncwarp();
-    drain_tile16(slot, g, block_size, b0, t * kTile, blocks, block_size, count, lane);
-    __syncwarp();
+    if (kWriteBack) {
+      drain_tile16(slot, g, block_size, b0, t * kTile, blocks, block_size, count, lane);
+      __syncwarp();
+    }
   }
 #undef ISSUE_BLOCK
   // the 32 block sums of this warp, added in double by a fixed butterfly: one value per warp
@@ -954,7 +1078,7 @@ moment_vec_kernel(float* __restrict__ g, const int8_t* __restrict__ moment_q,
   for (int offset = 16; offset > 0; offset >>= 1) warp_square += __shfl_xor_sync(0xffffffffu, warp_square, offset);
   if (lane == 0) block_partial[blockIdx.x] = warp_square;
   if (live) {
-    moment_scale[block] = __half_as_ushort(__float2half_rn(maximum / 127.0f));
+    (kWriteBack ? moment_scale : scale_out)[block] = __half_as_ushort(__float2half_rn(maximum / 127.0f));
   }
 }
 #undef QSTE_TILE_LOOP
@@ -966,7 +1090,7 @@ __global__ void publish_flips_kernel(const UpdateScalars* scalars, int64_t* flip
 }
 
 struct UpdateLayout {
-  size_t scalars, column_sum, row_stats, row_factor, column_factor, row_partial, block_partial, total;
+  size_t scalars, column_sum, row_stats, row_factor, column_factor, row_partial, block_partial, new_scale, total;
 };
 
 static UpdateLayout layout_for(int64_t R, int64_t C, int64_t blocks) {
@@ -979,6 +1103,7 @@ static UpdateLayout layout_for(int64_t R, int64_t C, int64_t blocks) {
   l.column_factor = at; at = align_up(at + sizeof(float) * (size_t)C, 256);
   l.row_partial = at; at = align_up(at + sizeof(double) * (size_t)R, 256);
   l.block_partial = at; at = align_up(at + sizeof(double) * (size_t)blocks, 256);
+  l.new_scale = at; at = align_up(at + sizeof(uint16_t) * (size_t)blocks, 256);
   l.total = at;
   return l;
 }
@@ -1009,6 +1134,7 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
   float* column_factor = reinterpret_cast<float*>(base + l.column_factor);
   double* row_partial = reinterpret_cast<double*>(base + l.row_partial);
   double* block_partial = reinterpret_cast<double*>(base + l.block_partial);
+  uint16_t* new_scale = reinterpret_cast<uint16_t*>(base + l.new_scale);
   const float beta1 = (float)beta1_in, beta2 = (float)beta2_in;
   const float update_clip = (float)update_clip_in, coordinate_lr = (float)coordinate_lr_in;
 
@@ -1044,29 +1170,44 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
                                                       row_partial, update_enabled);
   finish_update_norm_kernel<<<1, 1024, 0, stream>>>(row_partial, R, count, beta1, update_clip, scalars,
                                                     update_enabled);
-  if (recompute)
-    moment_vec_kernel<true><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, count, block_size,
-                                                            blocks, beta1, scalars, block_partial, update_enabled,
-                                                            C, row_factor, column_factor);
-  else if (vec_blocks)
-    moment_vec_kernel<false><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, count, block_size,
-                                                             blocks, beta1, scalars, block_partial, update_enabled,
-                                                             C, row_factor, column_factor);
-  else
-    moment_kernel<<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, count, block_size,
-                                                  blocks, beta1, scalars, block_partial, update_enabled);
-  finish_moment_norm_kernel<<<1, 1024, 0, stream>>>(block_partial, (int64_t)block_tiles, blocks, block_size,
-                                                    coordinate_lr, scalars, update_enabled);
   int block_shift = -1;
   if ((block_size & (block_size - 1)) == 0) {
     block_shift = 0;
     while (((int64_t)1 << block_shift) < block_size) ++block_shift;
   }
+  // lean: the fp32 moments are never stored; the last pass forms them again from the evidence
+  const bool lean = recompute && (C & 7) == 0 && block_shift >= 3;
+  if (lean)
+    moment_vec_kernel<true, false><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, new_scale, count,
+                                                                   block_size, blocks, beta1, scalars, block_partial,
+                                                                   update_enabled, C, row_factor, column_factor);
+  else if (recompute)
+    moment_vec_kernel<true, true><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, new_scale, count,
+                                                                  block_size, blocks, beta1, scalars, block_partial,
+                                                                  update_enabled, C, row_factor, column_factor);
+  else if (vec_blocks)
+    moment_vec_kernel<false, true><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, new_scale, count,
+                                                                   block_size, blocks, beta1, scalars, block_partial,
+                                                                   update_enabled, C, row_factor, column_factor);
+  else
+    moment_kernel<<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, count, block_size,
+                                                  blocks, beta1, scalars, block_partial, update_enabled);
+  finish_moment_norm_kernel<<<1, 1024, 0, stream>>>(block_partial, (int64_t)block_tiles, blocks, block_size,
+                                                    coordinate_lr, scalars, update_enabled);
   const int64_t bytes = R * ((C + 7) / 8);
   int64_t grid = ceil_div(bytes, 256);
   const int64_t cap = (int64_t)sm_count() * 16;
   if (grid > cap) grid = cap;
-  if ((C & 7) == 0 && block_shift >= 3)
+  int launched = 8;
+  if (lean) {
+    coordinate_and_pack_lean_kernel<<<(unsigned)grid, 256, 0, stream>>>(
+        gradient, coordinate, packed, moment_q, moment_scale, new_scale, row_factor, column_factor, bytes, C / 8,
+        block_shift, beta1, host_scramble((uint32_t)seed), step, step_device, scalars, update_enabled);
+    int64_t commit_grid = ceil_div(blocks, 256);
+    if (commit_grid > cap) commit_grid = cap;
+    commit_scales_kernel<<<(unsigned)commit_grid, 256, 0, stream>>>(new_scale, moment_scale, blocks, update_enabled);
+    launched = 9;
+  } else if ((C & 7) == 0 && block_shift >= 3)
     coordinate_and_pack_fast_kernel<<<(unsigned)grid, 256, 0, stream>>>(
         gradient, coordinate, packed, moment_q, moment_scale, bytes, block_shift,
         host_scramble((uint32_t)seed), step, step_device, scalars, update_enabled);
@@ -1075,7 +1216,7 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
         gradient, coordinate, packed, moment_q, moment_scale, R, C, block_shift, block_size,
         host_scramble((uint32_t)seed), step, step_device, scalars, update_enabled);
   if (flips_out) publish_flips_kernel<<<1, 1, 0, stream>>>(scalars, flips_out, update_enabled);
-  note_launches(flips_out ? 9 : 8);
+  note_launches(flips_out ? launched + 1 : launched);
   return launch_status("coordinate_update");
 }
 
@@ -1103,7 +1244,7 @@ constexpr int64_t kStaticMaxColumns = 16384;
 constexpr int64_t kStaticMaxBlocks = 262144;  // ceil(rows * columns / block_size)
 constexpr size_t kStaticScratchBytes =
     256 /*scalars*/ + 2 * 4 * kStaticMaxColumns + 2 * 4 * kStaticMaxRows + 8 * kStaticMaxRows +
-    8 * kStaticMaxBlocks + 7 * 256 /*alignment of each array*/;
+    8 * kStaticMaxBlocks + 2 * kStaticMaxBlocks + 8 * 256 /*alignment of each array*/;
 
 static __device__ __align__(256) unsigned char g_update_scratch[kStaticScratchBytes];
 
@@ -1155,7 +1296,8 @@ int qste_b200_coordinate_update_static(float* gradient, int8_t* coordinate, uint
   const int located = static_scratch_address(&scratch);
   if (located != QSTE_OK) return located;
   // Nothing in the scratch needs clearing here: every array is written in full before it is
-  // read within one call, and the flip counter is reset by the call's own second kernel.
+  // read within one call, and the flip counter is reset by the call's own third kernel
+  // (finish_factors_kernel).
   return run_coordinate_update(gradient, coordinate, packed, moment_q, moment_scale, row_v, col_v,
                                rows, columns, beta1, beta2, update_clip, coordinate_lr, block_size,
                                seed, step, step_device, update_enabled, flips_out, scratch,

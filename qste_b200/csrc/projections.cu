@@ -15,8 +15,8 @@ constexpr size_t kHeader = 256;  // workspace[0..8): device wait-timeout counter
 
 inline bool valid_dtype(int dtype) { return dtype_size(dtype) != 0; }
 
-// QSTE_B200_SMALL_BATCH=0 keeps batches of 1-128 on the kernels that served them before the
-// weight-stationary one existed (for A/B timing).
+// QSTE_B200_SMALL_BATCH=0 keeps batches of 1-4 on the kernels that served them before the
+// look-up-table kernel existed (for A/B timing).
 inline bool small_batch_auto() {
   static const bool enabled = !(getenv("QSTE_B200_SMALL_BATCH") && atoi(getenv("QSTE_B200_SMALL_BATCH")) == 0);
   return enabled;
@@ -44,23 +44,12 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
   cudaStream_t s = as_stream(stream);
   const int64_t pitch = (columns + 7) / 8;
 
-  // Small batches (all measured as CUDA-graph replays over rotating weight copies):
-  //   1-2 tokens   the look-up-table kernel (gemm_lut.cu): bits streamed once, a thread per weight row
-  //   3-4 tokens   the weight-stationary tcgen05 kernel (gemm_ws.cu) on wide, short matrices, else the
-  //                table kernel
-  //   5-128        the weight-stationary kernel where it wins (ws_preferred), else the large-batch tiles
-  const bool small_auto = path == QSTE_PATH_AUTO && small_batch_auto();
-  const bool ws_fits = ws_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype);
-  const bool ws_wins = small_auto && ws_fits && samples >= 3 && ws_preferred(samples, rows, columns);
-  if ((path == QSTE_PATH_STREAM || (small_auto && !ws_wins)) &&
+  // 1..4 tokens: the look-up-table kernel (gemm_lut.cu: bits streamed once, a thread per weight row,
+  // the contraction cut over a thread-block cluster); shapes it does not take fall to the older
+  // streaming kernel below, larger batches to the tensor-core tiles
+  if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) &&
       lut_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype))
     return lut_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, s);
-  if (path == QSTE_PATH_SMALL || ws_wins) {
-    if (!ws_fits) return QSTE_ERR_UNSUPPORTED;
-    if (!workspace || workspace_bytes < kHeader) return QSTE_ERR_WORKSPACE;
-    return ws_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, out_dtype,
-                      static_cast<unsigned long long*>(workspace), s);
-  }
   if (path == QSTE_PATH_STREAM ||
       (path == QSTE_PATH_AUTO && stream_single_launch(samples, columns) &&
        stream_supported(samples, rows, columns, packed))) {

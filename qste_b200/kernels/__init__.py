@@ -23,13 +23,12 @@ from . import _cabi, stream
 from .device import DeviceProfile, profile, warm
 
 _DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
-PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_STREAM, PATH_SMALL = 0, 1, 2, 3, 4
-_PATH_NAMES = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tensor": PATH_TENSOR, "stream": PATH_STREAM,
-               "small": PATH_SMALL}
+PATH_AUTO, PATH_SIMT, PATH_TENSOR, PATH_STREAM = 0, 1, 2, 3
+_PATH_NAMES = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tensor": PATH_TENSOR, "stream": PATH_STREAM}
 
 
 def _path() -> int:
-    """``QSTE_B200_PATH=auto|simt|tensor|stream|small`` pins the GEMM implementation (for tests)."""
+    """``QSTE_B200_PATH=auto|simt|tensor|stream`` pins the GEMM implementation (for tests)."""
 
     name = os.environ.get("QSTE_B200_PATH", "auto").strip().lower()
     if name not in _PATH_NAMES:
