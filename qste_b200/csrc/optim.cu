@@ -1083,6 +1083,84 @@ moment_vec_kernel(float* __restrict__ g, const int8_t* __restrict__ moment_q,
 }
 #undef QSTE_TILE_LOOP
 
+// ---------------------------------------------------------------------------
+// The moment pass when nothing is written back, by direct loads (no shared-memory tiles)
+// ---------------------------------------------------------------------------
+//
+// Once the moments are not stored (the lean path), the pass only READS: 4 bytes of evidence and
+// one of the old moment per coordinate.  A lane still owns one block of 256 coordinates -- its
+// sum of squares is one fp32 chain over the block in index order, as the reference forms it --
+// but it now fetches its kilobyte of evidence itself, 32 bytes per load (a whole sector: lanes
+// are a kilobyte apart, so nothing is shared between them), four loads of evidence and one of
+// moments in flight per 32 coordinates.  No tile ring means no shared memory per warp beyond the
+// column factors (staged once per CTA, padded by four floats per 256 so that the 32 lanes, whose
+// blocks start 256 columns apart, read them without bank conflicts), so the SM holds as many
+// warps as registers allow.  Requires block_size == 256 and columns % 256 == 0 (a block then
+// lies inside one row).
+__device__ __forceinline__ void ld_global_v8(const void* address, uint32_t* r) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(address));
+}
+
+constexpr int kDirectThreads = 256;
+
+__global__ void __launch_bounds__(kDirectThreads)
+moment_direct_kernel(const float* __restrict__ g, const int8_t* __restrict__ moment_q,
+                     const uint16_t* __restrict__ moment_scale, uint16_t* __restrict__ scale_out, int64_t blocks,
+                     int64_t C, float beta1, const UpdateScalars* __restrict__ scalars,
+                     double* __restrict__ block_partial, const uint8_t* update_enabled,
+                     const float* __restrict__ row_factor, const float* __restrict__ column_factor) {
+  if (disabled(update_enabled)) return;
+  extern __shared__ float factors[];   // column c at c + 4 * (c / 256)
+  for (int64_t c = threadIdx.x * 4; c < C; c += kDirectThreads * 4)
+    *reinterpret_cast<float4*>(factors + c + 4 * (c >> 8)) = *reinterpret_cast<const float4*>(column_factor + c);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (kDirectThreads / 32) + (threadIdx.x >> 5);
+  const int64_t block = warp * 32 + lane;
+  const bool live = block < blocks;
+  const int64_t start = (live ? block : 0) * 256;
+  const int64_t row = start / C;
+  const int64_t column0 = start - row * C;
+  const float multiplier = row_factor[row];
+  const float decay = __half2float(__ushort_as_half(moment_scale[live ? block : 0])) * beta1;
+  const float gain = scalars->gain;
+  const float* source = g + start;
+  const int8_t* previous = moment_q + start;
+  const float* factor = factors + column0 + 4 * (column0 >> 8);
+  float maximum = 1e-6f;
+  float block_square = 0.0f;
+#pragma unroll 2
+  for (int piece = 0; piece < 8; ++piece) {      // 32 coordinates per piece
+    uint32_t raw[4][8], old[8];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) ld_global_v8(source + piece * 32 + v * 8, raw[v]);
+    ld_global_v8(previous + piece * 32, old);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const float4 f0 = *reinterpret_cast<const float4*>(factor + piece * 32 + v * 8);
+      const float4 f1 = *reinterpret_cast<const float4*>(factor + piece * 32 + v * 8 + 4);
+      const float cf[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int index = v * 8 + e;
+        const int q = (int)(int8_t)((old[index >> 2] >> (8 * (index & 3))) & 0xffu);
+        const float update = __uint_as_float(raw[v][e]) * multiplier * cf[e];
+        const float moment = (float)q * decay + update * gain;
+        block_square += moment * moment;
+        maximum = fmaxf(maximum, fabsf(moment));
+      }
+    }
+  }
+  // the 32 block sums of this warp, added in double by the same fixed butterfly as the tiled kernel
+  double warp_square = live ? (double)block_square : 0.0;
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) warp_square += __shfl_xor_sync(0xffffffffu, warp_square, offset);
+  if (lane == 0 && warp * 32 < blocks) block_partial[warp] = warp_square;
+  if (live) scale_out[block] = __half_as_ushort(__float2half_rn(maximum / 127.0f));
+}
+
 __global__ void publish_flips_kernel(const UpdateScalars* scalars, int64_t* flips_out,
                                      const uint8_t* update_enabled) {
   if (disabled(update_enabled)) { *flips_out = 0; return; }
@@ -1177,7 +1255,24 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
   }
   // lean: the fp32 moments are never stored; the last pass forms them again from the evidence
   const bool lean = recompute && (C & 7) == 0 && block_shift >= 3;
-  if (lean)
+  const size_t factor_bytes = (size_t)(C + C / 64 + 8) * sizeof(float);
+  const bool direct = lean && block_size == 256 && C % 256 == 0 && aligned(gradient, 32) && aligned(moment_q, 32) &&
+                      factor_bytes <= 96 * 1024;
+  if (direct) {
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (factor_bytes > 48 * 1024 && (device < 0 || device >= 64 || !configured[device])) {
+      const cudaError_t error = cudaFuncSetAttribute(moment_direct_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     96 * 1024);
+      if (error != cudaSuccess) { set_last_cuda_error(error, "cudaFuncSetAttribute(moment_direct)"); return QSTE_ERR_CUDA; }
+      if (device >= 0 && device < 64) configured[device] = true;
+    }
+    const unsigned grid = (unsigned)ceil_div(blocks, kDirectThreads);
+    moment_direct_kernel<<<grid, kDirectThreads, factor_bytes, stream>>>(gradient, moment_q, moment_scale, new_scale, blocks,
+                                                                         C, beta1, scalars, block_partial, update_enabled,
+                                                                         row_factor, column_factor);
+  } else if (lean)
     moment_vec_kernel<true, false><<<block_tiles, 32, 0, stream>>>(gradient, moment_q, moment_scale, new_scale, count,
                                                                    block_size, blocks, beta1, scalars, block_partial,
                                                                    update_enabled, C, row_factor, column_factor);
