@@ -146,6 +146,49 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def step_trace(step, steps: int = 2) -> dict:
+    """Where a step's time goes: `steps` steps under the torch profiler (kernel times from CUPTI,
+    not a benchmark number), grouped by kind of kernel, with the busy and idle time of the
+    busiest stream (the compute stream).  Milliseconds per step."""
+
+    import collections
+
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as trace:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    events = [e for e in trace.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    duration = lambda e: e.device_time if hasattr(e, "device_time") else e.cuda_time  # noqa: E731
+    groups, streams = collections.Counter(), collections.defaultdict(list)
+    kinds = (("packed_gemm_tc", "packed-sign GEMMs"), ("prepare_rows", "gradient pre-pass"),
+             ("pack_affine", "pack_affine_rows"), ("smooth_", "packed activation kernels"),
+             ("split_finish", "GEMM tail kernels"), ("finish_inner", "GEMM tail kernels"),
+             ("nccl", "NCCL collectives"), ("Memcpy", "copies"))
+    update = ("row_squares", "column_squares", "precondition", "moment_", "coordinate_and_pack", "finish_factors",
+              "finish_update_norm", "finish_moment_norm", "commit_scales", "publish_flips")
+    for e in events:
+        name = e.name
+        kind = next((label for key, label in kinds if key in name), None)
+        if kind is None:
+            kind = "coordinate update kernels" if any(key in name for key in update) else \
+                "torch kernels (harness element-wise, norms, loss, AdamW)"
+        groups[kind] += duration(e)
+        streams[getattr(e, "device_resource_id", None)].append((e.time_range.start, e.time_range.end))
+    busiest = max(streams.values(), key=lambda spans: sum(b - a for a, b in spans))
+    busiest.sort()
+    idle = sum(max(0.0, busiest[i + 1][0] - busiest[i][1]) for i in range(len(busiest) - 1))
+    begin, end = min(a for spans in streams.values() for a, _ in spans), max(b for spans in streams.values() for _, b in spans)
+    per_step = lambda us: round(us / steps / 1e3, 3)  # noqa: E731
+    return {"steps": steps, "span_ms": per_step(end - begin),
+            "compute_stream_busy_ms": per_step(sum(b - a for a, b in busiest)), "compute_stream_idle_ms": per_step(idle),
+            "compute_stream_launches": len(busiest) // steps,
+            "other_streams_busy_ms": per_step(sum(b - a for spans in streams.values() if spans is not busiest for a, b in spans)),
+            "kernel_ms_by_kind": {kind: per_step(us) for kind, us in groups.most_common()}}
+
+
 def launch_count() -> int:
     from qste_b200.kernels import _cabi
 
@@ -305,6 +348,8 @@ def run_ours(args) -> dict:
         "wait_timeouts": kernels.wait_timeouts(device),
         "ranks_agree": bool(qdist.surfaces_agree(model)),
     }
+    if args.trace and rank == 0 and world == 1:
+        result["trace"] = step_trace(resident_step)
     if rank == 0 and not args.no_extras:
         # the kernels below are timed alone, against the burst peak: let the part leave the power
         # cap the step drove it into before timing them
@@ -1270,6 +1315,8 @@ def main() -> None:
                         help="with --workload kernel: which kernel to launch")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the per-kernel roofline section and the CPU baseline (profiling runs)")
+    parser.add_argument("--trace", action="store_true",
+                        help="mlp_stack on one GPU: add a profiler-based account of where a step's time goes")
     parser.add_argument("--tokens", type=int, default=0, help="tokens per GPU (default 16384)")
     parser.add_argument("--reserve", type=int, default=-1,
                         help="SMs the backward GEMMs leave to the all-reduce at N > 1 (default: the library's, 8)")

@@ -56,7 +56,8 @@ typedef enum {
   QSTE_PATH_AUTO = 0,   /* tcgen05 tensor-core kernel when the shape allows it, else the others */
   QSTE_PATH_SIMT = 1,   /* generic CUDA-core kernel (any shape) */
   QSTE_PATH_TENSOR = 2, /* tcgen05/TMEM kernel; QSTE_ERR_UNSUPPORTED when the shape does not fit */
-  QSTE_PATH_STREAM = 3  /* packed-bit streaming kernels on the CUDA cores, batches of 1-4 (forward only) */
+  QSTE_PATH_STREAM = 3  /* the small-batch forward kernels: look-up tables for 1-4 tokens, weights expanded in
+                           registers for 5-32 tokens of a 16-bit type (forward only) */
 } qste_path;
 
 int qste_b200_abi_version(void);
@@ -65,6 +66,10 @@ const char* qste_b200_status_string(int status);
 const char* qste_b200_last_cuda_error(void);
 /* Number of kernels this library has launched in this process so far. */
 unsigned long long qste_b200_launch_count(void);
+/* Which kernel family the calling thread's last qste_b200_packed_linear_affine ran: "lut" (1-4
+ * tokens), "mma" (5-32 tokens, 16-bit), "stream", "tensor" (tcgen05), "simt", or "" before the
+ * first call.  A diagnostic for tests and benchmarks; the reference has no counterpart. */
+const char* qste_b200_last_forward_kernel(void);
 /* The tensor-core GEMMs are persistent kernels with one block per SM.  A collective that runs
  * beside them on another stream (the evidence all-reduce of data-parallel training) finds no
  * free SM until a GEMM ends.  This sets how many SMs the GEMMs launched FROM THE CALLING THREAD
@@ -271,7 +276,7 @@ int qste_b200_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* pa
  * a host that binds this C ABI from a runtime whose device memory is one pre-planned arena
  * it does not own, or code that runs where entering the CUDA allocator is off limits (a
  * locked memory budget, a driver callback).  The scratch lives inside the library image as
- * a fixed device array (about 2.5 MB per GPU, held from library load to process exit), so
+ * a fixed device array (about 3 MB per GPU, held from library load to process exit), so
  * the call allocates nothing and takes no workspace.  Inputs, outputs and the in-place
  * state are still the caller's, exactly as in qste_b200_coordinate_update.
  *   - Limits: rows <= 16384, columns <= 16384 and ceil(rows * columns / block_size) <=

@@ -15,6 +15,8 @@ namespace qste {
 void set_last_cuda_error(cudaError_t error, const char* where);
 // Adds to the process-wide count of kernels this library has launched.
 void note_launches(int count);
+// Records which kernel family served the calling thread's forward (a string literal).
+void note_forward_kernel(const char* name);
 
 // Checks the launch that was just enqueued; returns a qste_status.
 inline int launch_status(const char* where) {

@@ -53,6 +53,13 @@ bool lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, co
 int lut_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,
                 const float* bias, int64_t rows, int64_t columns, void* out, cudaStream_t stream);
 
+// Forward for 5..32 tokens of a 16-bit type: warp-level MMAs with the weights expanded in registers
+// (gemm_mma.cu).
+bool mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x,
+                   const void* bits, const void* out, int out_dtype);
+int mma_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,
+                const float* bias, int64_t rows, int64_t columns, void* out, cudaStream_t stream);
+
 int simt_gemm(const void* A, int a_dtype, int64_t stride_ai, int64_t stride_ak, const uint8_t* bits,
               int64_t bit_pitch, int bits_row_is_k, const float* cs, const float* os,
               const float* ob, void* C, int c_dtype, int64_t I, int64_t J, int64_t K,

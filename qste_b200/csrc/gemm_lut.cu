@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include "cluster.cuh"
 #include "common.cuh"
 #include "gemm.h"
 
@@ -51,32 +52,6 @@ struct LutParams {
   int max_slice_groups;    // nibble groups (4 columns) of the widest slice: the table's extent
 };
 
-__device__ __forceinline__ uint32_t lut_cluster_rank() {
-  uint32_t rank;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  return rank;
-}
-__device__ __forceinline__ void lut_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
-  const uint32_t address = (uint32_t)__cvta_generic_to_shared(local);
-  float value;
-  asm volatile(
-      "{\n\t.reg .b32 remote;\n\t"
-      "mapa.shared::cluster.u32 remote, %1, %2;\n\t"
-      "ld.shared::cluster.f32 %0, [remote];\n\t}"
-      : "=f"(value) : "r"(address), "r"(rank) : "memory");
-  return value;
-}
-
-// slice `rank` of `slices` covers units [begin, end) of 128 columns, as evenly as they divide
-__device__ __forceinline__ void slice_units(int units, int slices, int rank, int& begin, int& end) {
-  begin = (int)((long long)units * rank / slices);
-  end = (int)((long long)units * (rank + 1) / slices);
-}
-
 template <typename T, int kM>
 __global__ void __launch_bounds__(kLutMaxThreads)
 packed_lut_forward_kernel(const __grid_constant__ LutParams p) {
@@ -85,7 +60,7 @@ packed_lut_forward_kernel(const __grid_constant__ LutParams p) {
   // look-up), then [kM][group_rows] partial sums
   float* table = lut_shared;
   float* partial = lut_shared + (size_t)kM * p.max_slice_groups * 16;
-  const int rank = (int)lut_cluster_rank();
+  const int rank = (int)cluster_rank();
   const long long cluster = blockIdx.x / p.slices;
   const long long row0 = cluster * p.group_rows;
   int unit_begin, unit_end;
@@ -188,7 +163,7 @@ packed_lut_forward_kernel(const __grid_constant__ LutParams p) {
   }
 
   // -- add the slices in rank order; each CTA finishes a share of the cluster's rows
-  lut_cluster_sync();
+  cluster_sync();
   for (int e = threadIdx.x; e < kM * share; e += blockDim.x) {
     const int m = e / share, row = rank * share + (e - m * share);
     const long long n = row0 + row;
@@ -201,7 +176,56 @@ packed_lut_forward_kernel(const __grid_constant__ LutParams p) {
     if (p.bias) value = value + (early ? early_bias : p.bias[n]);
     DType<T>::store(static_cast<T*>(p.out) + (long long)m * p.N + n, value);
   }
-  lut_cluster_sync();   // nobody leaves (and frees its shared memory) while a peer may still read it
+  cluster_sync();   // nobody leaves (and frees its shared memory) while a peer may still read it
+}
+
+constexpr size_t kLutSharedFloor = 116 * 1024;   // more than half an SM's shared memory: one CTA per SM
+
+// How many clusters of `cluster_size` CTAs of this kernel the device holds at once, every CTA on
+// an SM of its own (asked of the driver once per device and size: a GPC holds whole clusters only,
+// so it is fewer than SMs / size).
+template <typename T, int kM>
+int lut_cluster_capacity(int cluster_size) {
+  auto kernel = packed_lut_forward_kernel<T, kM>;
+  static int cached[64][4] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  const bool slot = device >= 0 && device < 64;
+  const int index = cluster_size <= 1 ? 0 : (cluster_size == 2 ? 1 : (cluster_size == 4 ? 2 : 3));
+  if (slot && cached[device][index] > 0) return cached[device][index];
+  const int by_count = sm_count() / cluster_size > 0 ? sm_count() / cluster_size : 1;
+  int clusters = 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)(cluster_size * sm_count()), 1, 1);
+    config.blockDim = dim3((unsigned)kLutMaxThreads, 1, 1);
+    config.dynamicSmemBytes = kLutSharedFloor;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = (unsigned)cluster_size;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) clusters = 0;
+  }
+  cudaGetLastError();
+  if (clusters <= 0) clusters = by_count * 3 / 4 > 0 ? by_count * 3 / 4 : 1;
+  if (clusters > by_count) clusters = by_count;
+  if (slot) cached[device][index] = clusters;
+  return clusters;
+}
+
+int lut_cluster_capacity(int dtype, int tokens, int cluster_size) {
+  int capacity = 0;
+  QSTE_DISPATCH_DTYPE(dtype, T, {
+    switch (tokens) {
+      case 1: capacity = lut_cluster_capacity<T, 1>(cluster_size); break;
+      case 2: capacity = lut_cluster_capacity<T, 2>(cluster_size); break;
+      default: capacity = lut_cluster_capacity<T, 4>(cluster_size); break;
+    }
+  });
+  return capacity;
 }
 
 template <typename T, int kM>
@@ -240,13 +264,12 @@ struct LutPlan {
   bool ok;
 };
 
-LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns) {
+LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns, int dtype) {
   LutPlan plan = {};
   plan.ok = false;
   if (samples < 1 || samples > 4 || rows < 1 || columns < 128 || columns % 128 != 0) return plan;
   plan.tokens = samples <= 1 ? 1 : (samples <= 2 ? 2 : 4);
   const int units = (int)(columns / 128);
-  const int sms = sm_count();
   // Four slices up to 4096 columns, eight beyond (measured at one token, 4096 -> 14336: 12.8 us with
   // four, 16.0 with eight; 14336 -> 4096: 15.3 against 14.1): a row's slice is then 64-128 bytes of
   // bits, and a matrix with few rows still gives every SM a few hundred threads.
@@ -258,7 +281,7 @@ LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns) {
     // the table is indexed a whole chunk (8 vectors = 8 units) at a time: round its extent up
     const int table_units = (widest + kLutChunk - 1) / kLutChunk * kLutChunk;
     const size_t table_bytes = (size_t)plan.tokens * table_units * 32 * 16 * sizeof(float);
-    int clusters = sms / s;
+    int clusters = lut_cluster_capacity(dtype, plan.tokens, s);   // resident at once, a CTA per SM
     if (clusters < 1) clusters = 1;
     int group_rows = (int)ceil_div(rows, clusters);
     clusters = (int)ceil_div(rows, group_rows);
@@ -284,6 +307,8 @@ LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns) {
     if (threads < 128) threads = 128;
     plan.threads = threads;
     plan.shared = (size_t)plan.tokens * plan.max_slice_groups * 16 * sizeof(float) + (size_t)plan.tokens * group_rows * sizeof(float);
+    // two CTAs on one SM would each run at half speed while other SMs idle
+    if (plan.shared < kLutSharedFloor) plan.shared = kLutSharedFloor;
     plan.ok = true;
     return plan;
   }
@@ -297,12 +322,12 @@ bool lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, co
   if (dtype_size(dtype) == 0 || out_dtype != dtype) return false;
   if (!aligned(bits, 16) || !aligned(x, 2) || !aligned(out, 2)) return false;
   if (check_arch() != QSTE_OK) return false;
-  return lut_plan(samples, rows, columns).ok;
+  return lut_plan(samples, rows, columns, dtype).ok;
 }
 
 int lut_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale, const float* bias,
                 int64_t rows, int64_t columns, void* out, cudaStream_t stream) {
-  const LutPlan plan = lut_plan(samples, rows, columns);
+  const LutPlan plan = lut_plan(samples, rows, columns, dtype);
   if (!plan.ok) return QSTE_ERR_UNSUPPORTED;
   LutParams params = {};
   params.x = x; params.bits = packed; params.scale = scale; params.bias = bias; params.out = out;

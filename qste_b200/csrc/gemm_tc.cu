@@ -368,6 +368,8 @@ packed_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile uint32_t* queue_ring = tmem_slot + 2;
   const uint32_t queue_ring_address = smem_u32(tmem_slot + 2);
+  // odd CTA of a pair: how many of its readers have read queue word i
+  const uint32_t handback_address = smem_u32(tmem_slot + 2 + kQueue);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool a_mn_major = p.kind == TC_EVIDENCE;
@@ -381,7 +383,10 @@ packed_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const bool dynamic = p.schedule != nullptr;
   // readers of a queue word: MMA thread (or relay), 16 expander warps, 4 epilogue warps, and the
   // odd CTA's TMA thread
-  constexpr int kQueueReaders = (1 + kExpanderWarps + kEpilogueWarps) * Shape::kCtas + (kIsPair ? 1 : 0);
+  constexpr int kCtaReaders = 1 + kExpanderWarps + kEpilogueWarps;
+  constexpr uint32_t kOddReaders = kCtaReaders + 1;
+  // arrivals on queue_empty: this CTA's readers, plus one from the odd CTA of a pair (its last reader)
+  constexpr int kQueueReaders = kCtaReaders + (kIsPair ? 1 : 0);
   // accumulator buffers in flight: the tall tile uses both halves of TMEM at once
   constexpr int kMembers = Shape::kMembers;
 
@@ -400,6 +405,7 @@ packed_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       mbar_init(queue_empty(i), kQueueReaders);
     }
     *abort_flag = 0;
+    for (int i = 0; i < kQueue; ++i) tmem_slot[2 + kQueue + i] = 0;
     fence_barrier_init();
   }
   if (warp == kTmaWarp) {
@@ -427,11 +433,16 @@ packed_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   // The lt-th item of this CTA (pair), or -1 when there is none (or the kernel is giving up).
   // Called by every lane of a warp role, or by the one active lane of a single-thread role.  One
   // lane waits, reads the word and hands the slot back; a warp role gets the value by shuffle.
-  // The address of the arrive that hands the slot back is made to depend on the word read, so
-  // the word is in a register before the arrive can issue.  Without that, readers of the odd CTA
-  // were seen to read a slot AFTER the producer had refilled it: their arrive is a release at CTA
-  // scope only, the producer sits in the other CTA, and nothing else ordered the load before it.
-  // (It took items of a single k-block to show: only then is the producer a full ring ahead.)
+  // The producer sits in the even CTA.  A reader there hands back with an arrive on the producer's
+  // own barrier (a release at CTA scope, which the producer's wait acquires).  The readers of the
+  // odd CTA count themselves in their own shared memory with an acquire-release atomic at CTA
+  // scope, and the last of them passes the slot back with ONE remote arrive that releases at
+  // cluster scope; the producer's wait acquires at cluster scope.  Every reader's load of the word
+  // is thus ordered before the refill by the memory model, and only one thread per item pays for
+  // the cluster-scope release (all 22 paying it cost 0.8 % of a large GEMM).  With a CTA-scope
+  // remote arrive from each reader, readers of the odd CTA were seen to read a slot AFTER it had
+  // been refilled; it took items of a single k-block to show, only then is the producer a full ring
+  // ahead.
   auto take = [&](int lt, bool whole_warp) -> int {
     if (!dynamic) {
       const int q = worker + lt * workers;
@@ -442,9 +453,17 @@ packed_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (!whole_warp || lane == 0) {
       if (WAIT(queue_full(slot), (lt / kQueue) & 1)) {
         const uint32_t word = queue_ring[slot];
-        const uint32_t bar = queue_empty(slot) + ((word >> 31) << 3);  // word < 2^31: adds nothing
-        if (rank == 0) mbar_arrive(bar);
-        else mbar_arrive_remote(bar, 0);
+        if (rank == 0) {
+          mbar_arrive(queue_empty(slot));
+        } else {
+          uint32_t before;
+          asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;"
+                       : "=r"(before) : "r"(handback_address + 4u * slot) : "memory");
+          if (before == kOddReaders - 1) {
+            asm volatile("st.relaxed.cta.shared::cta.u32 [%0], %1;" ::"r"(handback_address + 4u * slot), "r"(0u) : "memory");
+            mbar_arrive_remote_release(queue_empty(slot), 0);
+          }
+        }
         q = (int)word < p.items ? (int)word : -1;
       }
     }

@@ -23,6 +23,8 @@
 // The reference's hand-written loops run on one thread (its extension is built
 // without OpenMP, so at::parallel_for is a plain call); that single-thread order
 // is the one reproduced.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace qste {
@@ -32,7 +34,7 @@ constexpr int kTile = 32;
 constexpr int kPitch = kTile + 1;
 
 struct UpdateScalars {           // lives at the start of the workspace
-  unsigned long long reserved;   // +0
+  unsigned long long reserved;   // +0  (the GEMM kernels count their abandoned waits here)
   long long flips;               // +8
   float gain;                    // +16  (1 - beta1) / update_divisor
   float coordinate_step;         // +20  coordinate_lr / moment_rms
@@ -744,13 +746,11 @@ __device__ __forceinline__ void drain_tile16(float (*slot)[kTile], float* __rest
     cp_async_wait<kStages - 1>();                                          \
     __syncwarp();
 
-__global__ void __launch_bounds__(32)
-row_squares_vec_kernel(const float* __restrict__ g, int64_t R, int64_t C, uint16_t* __restrict__ row_v,
-                       float* __restrict__ row_stats, float beta2, const uint8_t* update_enabled) {
-  if (disabled(update_enabled)) return;
-  __shared__ __align__(16) float ring[kStages][kTile][kTile];
-  const int lane = threadIdx.x;
-  const int64_t r0 = (int64_t)blockIdx.x * kTile;
+// one warp: the sums of squares of rows 32 * tile .. + 31, and their moving average
+__device__ __forceinline__ void row_squares_tile(float (*ring)[kTile][kTile], const float* __restrict__ g, int64_t R,
+                                                 int64_t C, uint16_t* __restrict__ row_v,
+                                                 float* __restrict__ row_stats, float beta2, int64_t tile, int lane) {
+  const int64_t r0 = tile * kTile;
   const int64_t tiles = (C + kTile - 1) / kTile;
   const int64_t limit = R * C;
   float total = 0.0f;
@@ -775,6 +775,14 @@ row_squares_vec_kernel(const float* __restrict__ g, int64_t R, int64_t C, uint16
     row_stats[row] = updated;
     row_v[row] = __half_as_ushort(__float2half_rn(updated));
   }
+}
+
+__global__ void __launch_bounds__(32)
+row_squares_vec_kernel(const float* __restrict__ g, int64_t R, int64_t C, uint16_t* __restrict__ row_v,
+                       float* __restrict__ row_stats, float beta2, const uint8_t* update_enabled) {
+  if (disabled(update_enabled)) return;
+  __shared__ __align__(16) float ring[kStages][kTile][kTile];
+  row_squares_tile(ring, g, R, C, row_v, row_stats, beta2, blockIdx.x, threadIdx.x);
 }
 
 __global__ void __launch_bounds__(32)
@@ -806,13 +814,10 @@ column_squares_vec_kernel(const float* __restrict__ g, int64_t R, int64_t C,
 // every address that does not depend on the tile is computed once.  With one chain per column
 // there are only C / 32 warps, fewer than SMs at the sizes that matter, so what counts is the
 // number of instructions a warp spends per row beside the chain's own add.
-__global__ void __launch_bounds__(32)
-column_squares_interior_kernel(const float* __restrict__ g, int64_t R, int64_t C,
-                               float* __restrict__ column_sum, const uint8_t* update_enabled) {
-  if (disabled(update_enabled)) return;
-  __shared__ __align__(16) float ring[kStages][kTile][kTile];
-  const int lane = threadIdx.x;
-  const int64_t c0 = (int64_t)blockIdx.x * kTile;
+__device__ __forceinline__ void column_squares_strip(float (*ring)[kTile][kTile], const float* __restrict__ g,
+                                                     int64_t R, int64_t C, float* __restrict__ column_sum,
+                                                     int64_t strip, int lane) {
+  const int64_t c0 = strip * kTile;
   const int tiles = (int)(R / kTile);
   // this lane copies 16 bytes of rows lane / 8, lane / 8 + 4, ... of a tile
   const int chunk = lane & 7, sub = lane >> 3;
@@ -856,6 +861,31 @@ column_squares_interior_kernel(const float* __restrict__ g, int64_t R, int64_t C
     __syncwarp();
   }
   column_sum[c0 + lane] = total;
+}
+
+__global__ void __launch_bounds__(32)
+column_squares_interior_kernel(const float* __restrict__ g, int64_t R, int64_t C,
+                               float* __restrict__ column_sum, const uint8_t* update_enabled) {
+  if (disabled(update_enabled)) return;
+  __shared__ __align__(16) float ring[kStages][kTile][kTile];
+  column_squares_strip(ring, g, R, C, column_sum, blockIdx.x, threadIdx.x);
+}
+
+// Both factor sums in one launch: CTAs [0, C / 32) are the column strips -- few, long, and light
+// on bandwidth -- and the rest the row tiles, which are many, short and bandwidth-hungry, in the
+// SMs' spare room.  The two read the evidence independently, so side by side they take about as
+// long as the slower one instead of the sum of both.
+__global__ void __launch_bounds__(32)
+factor_sums_kernel(const float* __restrict__ g, int64_t R, int64_t C, float* __restrict__ column_sum,
+                   uint16_t* __restrict__ row_v, float* __restrict__ row_stats, float beta2,
+                   const uint8_t* update_enabled) {
+  if (disabled(update_enabled)) return;
+  __shared__ __align__(16) float ring[kStages][kTile][kTile];
+  const int64_t column_tiles = C / kTile;
+  if (blockIdx.x < column_tiles)
+    column_squares_strip(ring, g, R, C, column_sum, blockIdx.x, threadIdx.x);
+  else
+    row_squares_tile(ring, g, R, C, row_v, row_stats, beta2, blockIdx.x - column_tiles, threadIdx.x);
 }
 
 __global__ void __launch_bounds__(32)
@@ -1186,6 +1216,13 @@ static UpdateLayout layout_for(int64_t R, int64_t C, int64_t blocks) {
   return l;
 }
 
+// QSTE_B200_FACTOR_SUMS=separate: the row and the column sums of squares as two launches even when
+// both sides are multiples of 32 (for A/B timing; one launch is 30 us faster at 14336 x 4096).
+static bool separate_factor_sums() {
+  static const bool separate = getenv("QSTE_B200_FACTOR_SUMS") != nullptr;
+  return separate;
+}
+
 uint32_t host_scramble(uint32_t value) {
   value = (value ^ 61u) ^ (value >> 16);
   value += value << 3;
@@ -1219,14 +1256,20 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
   const unsigned row_tiles = (unsigned)ceil_div(R, kTile);
   const unsigned column_tiles = (unsigned)ceil_div(C, kTile);
   const unsigned block_tiles = (unsigned)ceil_div(blocks, kTile);
+  int launched_less = 0;
 
   // 16-byte aligned rows (of the matrix and of the [blocks, block_size] view): vectorised tiles
   const bool vec_rows = (C % 4 == 0) && aligned(gradient, 16);
   const bool vec_blocks = (block_size % 32 == 0) && (count % 4 == 0) && aligned(gradient, 16) &&
                           aligned(moment_q, 16);
-  if (vec_rows) {
+  const bool interior = R % kTile == 0 && C % kTile == 0;
+  if (vec_rows && interior && !separate_factor_sums()) {
+    factor_sums_kernel<<<column_tiles + row_tiles, 32, 0, stream>>>(gradient, R, C, column_sum, row_v, row_stats, beta2,
+                                                                    update_enabled);
+    launched_less = 1;
+  } else if (vec_rows) {
     row_squares_vec_kernel<<<row_tiles, 32, 0, stream>>>(gradient, R, C, row_v, row_stats, beta2, update_enabled);
-    if (R % kTile == 0 && C % kTile == 0)
+    if (interior)
       column_squares_interior_kernel<<<column_tiles, 32, 0, stream>>>(gradient, R, C, column_sum, update_enabled);
     else
       column_squares_vec_kernel<<<column_tiles, 32, 0, stream>>>(gradient, R, C, column_sum, update_enabled);
@@ -1311,7 +1354,7 @@ int run_coordinate_update(float* gradient, int8_t* coordinate, uint8_t* packed, 
         gradient, coordinate, packed, moment_q, moment_scale, R, C, block_shift, block_size,
         host_scramble((uint32_t)seed), step, step_device, scalars, update_enabled);
   if (flips_out) publish_flips_kernel<<<1, 1, 0, stream>>>(scalars, flips_out, update_enabled);
-  note_launches(flips_out ? launched + 1 : launched);
+  note_launches((flips_out ? launched + 1 : launched) - launched_less);
   return launch_status("coordinate_update");
 }
 

@@ -15,8 +15,8 @@ constexpr size_t kHeader = 256;  // workspace[0..8): device wait-timeout counter
 
 inline bool valid_dtype(int dtype) { return dtype_size(dtype) != 0; }
 
-// QSTE_B200_SMALL_BATCH=0 keeps batches of 1-4 on the kernels that served them before the
-// look-up-table kernel existed (for A/B timing).
+// QSTE_B200_SMALL_BATCH=0 keeps batches of 1-32 on the kernels that served them before the
+// look-up-table and register-expansion kernels existed (for A/B timing).
 inline bool small_batch_auto() {
   static const bool enabled = !(getenv("QSTE_B200_SMALL_BATCH") && atoi(getenv("QSTE_B200_SMALL_BATCH")) == 0);
   return enabled;
@@ -48,12 +48,21 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
   // the contraction cut over a thread-block cluster); shapes it does not take fall to the older
   // streaming kernel below, larger batches to the tensor-core tiles
   if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) &&
-      lut_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype))
+      lut_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype)) {
+    note_forward_kernel("lut");
     return lut_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, s);
+  }
+  // 5..32 tokens of a 16-bit type: weights expanded in registers, warp-level MMAs (gemm_mma.cu)
+  if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) &&
+      mma_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype)) {
+    note_forward_kernel("mma");
+    return mma_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, s);
+  }
   if (path == QSTE_PATH_STREAM ||
       (path == QSTE_PATH_AUTO && stream_single_launch(samples, columns) &&
        stream_supported(samples, rows, columns, packed))) {
     if (!stream_supported(samples, rows, columns, packed)) return QSTE_ERR_UNSUPPORTED;
+    note_forward_kernel("stream");
     return stream_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, out_dtype, s);
   }
   if (path == QSTE_PATH_TENSOR || path == QSTE_PATH_AUTO) {
@@ -69,10 +78,12 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
       p.I = samples; p.J = rows; p.K = columns;
       p.workspace = static_cast<char*>(workspace) + kHeader;
       p.diagnostics = static_cast<unsigned long long*>(workspace);
+      note_forward_kernel("tensor");
       return tc_run(p, s);
     }
     if (path == QSTE_PATH_TENSOR) return QSTE_ERR_UNSUPPORTED;
   }
+  note_forward_kernel("simt");
   return simt_gemm(inputs, dtype, columns, 1, packed, pitch, 0, nullptr, scale, bias, out, out_dtype,
                    samples, rows, columns, s);
 }

@@ -15,6 +15,10 @@ void set_last_cuda_error(cudaError_t error, const char* where) {
            cudaGetErrorString(error));
 }
 
+// the kernel family the calling thread's last forward ran (see qste_b200_last_forward_kernel)
+static thread_local const char* g_last_forward = "";
+void note_forward_kernel(const char* name) { g_last_forward = name; }
+
 static std::atomic<unsigned long long> g_launches{0};
 void note_launches(int count) { g_launches.fetch_add((unsigned long long)count, std::memory_order_relaxed); }
 
@@ -95,6 +99,8 @@ int qste_b200_set_reserved_sms(int count) {
   qste::g_reserved_sms = count > 0 ? count : 0;
   return previous;
 }
+
+const char* qste_b200_last_forward_kernel(void) { return qste::g_last_forward; }
 
 unsigned long long qste_b200_launch_count(void) { return qste::g_launches.load(std::memory_order_relaxed); }
 

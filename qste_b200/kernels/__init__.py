@@ -149,6 +149,13 @@ def first_wait_timeout(device=None) -> dict | None:
     return {"line": word >> 32, "block": (word >> 16) & 0xFFFF, "thread": thread, "warp": thread // 32}
 
 
+def last_forward_kernel() -> str:
+    """The kernel family this thread's last ``packed_linear_affine`` ran: ``"lut"`` (1-4 tokens),
+    ``"mma"`` (5-32 tokens of a 16-bit type), ``"stream"``, ``"tensor"`` (tcgen05) or ``"simt"``."""
+
+    return _cabi.load().qste_b200_last_forward_kernel().decode()
+
+
 def _check_packed(packed: Tensor, columns: int, what: str) -> None:
     if packed.dtype != torch.uint8 or packed.dim() != 2:
         raise RuntimeError(f"{what}: packed signs must be a rank-2 uint8 tensor")
@@ -757,5 +764,5 @@ __all__ = [
     "pack_coordinate", "pack_affine_rows", "packed_embedding", "packed_linear_affine",
     "packed_row_inner", "packed_transpose", "profile", "set_backward_reserve", "smooth_backward", "smooth_forward",
     "smooth_supported", "status", "stream", "unpack_bits",
-    "unpack_rows", "wait_timeouts", "warm", "warn_if_slow", "first_wait_timeout", "check_waits",
+    "unpack_rows", "wait_timeouts", "warm", "warn_if_slow", "first_wait_timeout", "check_waits", "last_forward_kernel",
 ]

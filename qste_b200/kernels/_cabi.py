@@ -18,6 +18,7 @@ SYMBOLS = (
     "qste_b200_status_string",
     "qste_b200_last_cuda_error",
     "qste_b200_launch_count",
+    "qste_b200_last_forward_kernel",
     "qste_b200_set_reserved_sms",
     "qste_b200_pack_coordinate",
     "qste_b200_pack_affine_rows",
@@ -57,6 +58,7 @@ _SIGNATURES = {
     "qste_b200_status_string": (ctypes.c_char_p, [_int]),
     "qste_b200_last_cuda_error": (ctypes.c_char_p, []),
     "qste_b200_launch_count": (ctypes.c_ulonglong, []),
+    "qste_b200_last_forward_kernel": (ctypes.c_char_p, []),
     "qste_b200_set_reserved_sms": (_int, [_int]),
     "qste_b200_pack_coordinate": (_int, [_p, _i64, _i64, _p, _p]),
     "qste_b200_pack_affine_rows": (_int, [_p, _int, _i64, _i64, _p, _p, _p, _p]),

@@ -242,6 +242,47 @@ def test_look_up_table_forward_for_one_to_four_tokens(samples, rows, columns, dt
     assert rel(host(y_nobias), like(oracle.packed_linear_affine(x.float(), bits, scale, None, columns), dtype)) <= bar
 
 
+@pytest.mark.parametrize("samples", [5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (4104, 2048), (300, 12288),
+                                          (14336, 4096), (4096, 14336), (11008, 4096), (5632, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_register_expansion_forward_for_5_to_32_tokens(samples, rows, columns, dtype):
+    """The warp-MMA kernel of gemm_mma.cu against the oracle: every count of token tiles (1, 2, 4)
+    at its first and last batch size, row counts that do not divide over the clusters or the 16-row
+    slabs, contractions from one unit of 128 columns (one CTA per cluster) to 14336 (eight), runs of
+    512 columns that are partly filled (768, 14336 / 8), with and without bias -- through the
+    dispatcher's own choice (no forced path), which must be this kernel wherever it is meant to
+    serve: up to 16 tokens always, up to 32 for contractions of at most 12288 columns."""
+
+    x, _, bits, scale, bias = _problem(samples, rows, columns, dtype, seed=samples + rows)
+    y = kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
+    served = kernels.last_forward_kernel()
+    assert served == ("mma" if samples <= 16 or columns <= 12288 else "tensor")
+    y_nobias = kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), None, columns)
+    assert y.dtype == dtype and y.shape == (samples, rows)
+    want = oracle.packed_linear_affine(x.float(), bits, scale, bias, columns)
+    assert rel(host(y), like(want, dtype)) <= 1e-3
+    assert rel(host(y_nobias), like(oracle.packed_linear_affine(x.float(), bits, scale, None, columns), dtype)) <= 1e-3
+    # and element by element: the same sums in another order, rounded once to the 16-bit type
+    apart = np.abs(host(y) - like(want, dtype))
+    assert float(apart.max()) <= 2.0 ** -6 * float(np.abs(like(want, dtype)).max())
+
+
+def test_small_batch_forward_dispatch():
+    """Which kernel family serves which batch size at a layer's shape (bf16)."""
+
+    rows, columns = 4096, 4096
+    chosen = {}
+    for samples in (1, 4, 5, 32, 33, 128):
+        x, _, bits, scale, bias = _problem(samples, rows, columns, torch.bfloat16, seed=samples)
+        kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
+        chosen[samples] = kernels.last_forward_kernel()
+    assert chosen == {1: "lut", 4: "lut", 5: "mma", 32: "mma", 33: "tensor", 128: "tensor"}
+    x, _, bits, scale, bias = _problem(16, rows, columns, torch.float32, seed=3)
+    kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
+    assert kernels.last_forward_kernel() == "tensor"      # fp32 activations: three bf16 planes on tcgen05
+
+
 TENSOR_SHAPES = [(128, 256, 128), (200, 300, 256), (1024, 512, 1024), (77, 1000, 384), (4096, 2048, 2048)]
 # Shapes whose output has at least 148 tiles of 256 x 256, ragged on both sides: the kernel then
 # runs its 256-row tiles, two or three per CTA, with the expander warps sharing the epilogue.
