@@ -56,8 +56,8 @@ typedef enum {
   QSTE_PATH_AUTO = 0,   /* tcgen05 tensor-core kernel when the shape allows it, else the others */
   QSTE_PATH_SIMT = 1,   /* generic CUDA-core kernel (any shape) */
   QSTE_PATH_TENSOR = 2, /* tcgen05/TMEM kernel; QSTE_ERR_UNSUPPORTED when the shape does not fit */
-  QSTE_PATH_STREAM = 3  /* the small-batch forward kernels: look-up tables for 1-4 tokens, weights expanded in
-                           registers for 5-32 tokens of a 16-bit type (forward only) */
+  QSTE_PATH_STREAM = 3  /* the small-batch forward kernels: look-up tables for 1-2 tokens (1-4 of fp32), weights expanded in
+                           registers for 3-32 tokens of a 16-bit type (forward only) */
 } qste_path;
 
 int qste_b200_abi_version(void);
@@ -66,8 +66,8 @@ const char* qste_b200_status_string(int status);
 const char* qste_b200_last_cuda_error(void);
 /* Number of kernels this library has launched in this process so far. */
 unsigned long long qste_b200_launch_count(void);
-/* Which kernel family the calling thread's last qste_b200_packed_linear_affine ran: "lut" (1-4
- * tokens), "mma" (5-32 tokens, 16-bit), "stream", "tensor" (tcgen05), "simt", or "" before the
+/* Which kernel family the calling thread's last qste_b200_packed_linear_affine ran: "lut" (1-2
+ * tokens), "mma" (3-32 tokens, 16-bit), "stream", "tensor" (tcgen05), "simt", or "" before the
  * first call.  A diagnostic for tests and benchmarks; the reference has no counterpart. */
 const char* qste_b200_last_forward_kernel(void);
 /* The tensor-core GEMMs are persistent kernels with one block per SM.  A collective that runs

@@ -47,13 +47,17 @@ bool tc_supported(int kind, int64_t I, int64_t J, int64_t K, int dtype, const vo
                   const void* bits, const void* out, int out_dtype);
 int tc_run(const TcProblem& problem, cudaStream_t stream);
 
-// Forward for 1..4 tokens on the CUDA cores, bound by streaming the bits (gemm_lut.cu).
+// The largest batch of a 16-bit type the look-up-table kernel serves (2); the register-expansion
+// kernel takes over above it.  QSTE_B200_LUT_TOKENS=n (0..4) moves the hand-over (for A/B timing).
+int lut_max_tokens();
+
+// Forward for 1..2 tokens (1..4 of fp32) on the CUDA cores, bound by streaming the bits (gemm_lut.cu).
 bool lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x,
                    const void* bits, const void* out, int out_dtype);
 int lut_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,
                 const float* bias, int64_t rows, int64_t columns, void* out, cudaStream_t stream);
 
-// Forward for 5..32 tokens of a 16-bit type: warp-level MMAs with the weights expanded in registers
+// Forward for 3..32 tokens of a 16-bit type: warp-level MMAs with the weights expanded in registers
 // (gemm_mma.cu).
 bool mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x,
                    const void* bits, const void* out, int out_dtype);

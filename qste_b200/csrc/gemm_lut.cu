@@ -1,5 +1,5 @@
-// Forward of the binary Linear for a handful of tokens (1..4), on the CUDA cores, bound by
-// streaming the sign bits (sm_100a).
+// Forward of the binary Linear for one or two tokens (up to four of fp32), on the CUDA cores,
+// bound by streaming the sign bits (sm_100a).
 //
 //   Y[m, n] = (sum_k X[m, k] * sign(W)[n, k]) * scale[n] + bias[n]
 //
@@ -267,7 +267,8 @@ struct LutPlan {
 LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns, int dtype) {
   LutPlan plan = {};
   plan.ok = false;
-  if (samples < 1 || samples > 4 || rows < 1 || columns < 128 || columns % 128 != 0) return plan;
+  // fp32 activations have no register-expansion kernel to hand over to: the tables serve them up to four tokens
+  if (samples < 1 || samples > (dtype == QSTE_F32 ? 4 : lut_max_tokens()) || rows < 1 || columns < 128 || columns % 128 != 0) return plan;
   plan.tokens = samples <= 1 ? 1 : (samples <= 2 ? 2 : 4);
   const int units = (int)(columns / 128);
   // Four slices up to 4096 columns, eight beyond (measured at one token, 4096 -> 14336: 12.8 us with
@@ -316,6 +317,15 @@ LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns, int dtype) {
 }
 
 }  // namespace
+
+int lut_max_tokens() {
+  static const int tokens = [] {
+    const char* text = getenv("QSTE_B200_LUT_TOKENS");
+    const int value = text ? atoi(text) : 2;
+    return value < 0 ? 0 : (value > 4 ? 4 : value);
+  }();
+  return tokens;
+}
 
 bool lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* x, const void* bits,
                    const void* out, int out_dtype) {

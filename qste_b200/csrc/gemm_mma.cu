@@ -1,4 +1,4 @@
-// Forward of the binary Linear for 5..32 tokens with the weights held in registers (sm_100a).
+// Forward of the binary Linear for 3..32 tokens with the weights held in registers (sm_100a).
 //
 //   Y[m, n] = (sum_k X[m, k] * sign(W)[n, k]) * scale[n] + bias[n]
 //
@@ -12,9 +12,10 @@
 // of the instruction with one shift and one logic operation, straight from the words it loaded
 // from global memory, so the expanded weights never exist anywhere.
 //
-//   * A warp owns two slabs of 16 weight rows.  Lane 4g + q holds rows g and g + 8 of each slab and
-//     loads, of every run of 512 columns, the 16 bytes of unit q (128 columns): the four lanes of a
-//     row share the run out between them and nothing is loaded twice.
+//   * A warp owns a slab of 16 weight rows.  Lane 4g + q holds rows g and g + 8 of it and loads, of
+//     every run of 512 columns, the 16 bytes of unit q (128 columns): the four lanes of a row share
+//     the run out between them and nothing is loaded twice.  (Two slabs per warp, sharing the
+//     activation fragments, were 5-30 % slower: half as many warps to hide latency with.)
 //   * The order of the contraction index inside an MMA is free as long as both operands agree, so
 //     it is chosen to suit the bits: in step (c, p) of a run -- word c of the unit, p = 0..7 -- lane q
 //     supplies columns p, p + 16 (first k-pair of its quad slot) and p + 8, p + 24 (second) of word c
@@ -24,7 +25,7 @@
 //   * The activations are the B operand: tokens are the `n` of the instruction (8 per tile, 1-4
 //     tiles).  They are staged in shared memory ONCE per CTA in the matching order -- a 16-byte
 //     chunk per (step, k-half) holding, for q = 0..3, the two columns lane q pairs up -- and read
-//     with `ldmatrix` (rows padded by 16 bytes: no bank conflicts) for both slabs.
+//     with `ldmatrix` (rows padded by 16 bytes: no bank conflicts).
 //   * The contraction is cut into S slices over the S CTAs of a thread-block cluster (S = 1, 2, 4
 //     or 8): partial sums stay in shared memory, and after a cluster barrier every CTA adds the S
 //     partials of its share of the rows in rank order through distributed shared memory, applies
@@ -47,8 +48,8 @@
 namespace qste {
 namespace {
 
-constexpr int kMmaMaxThreads = 512;
-constexpr int kSlabs = 2;                    // slabs of 16 weight rows per warp
+constexpr int kMmaMaxThreads = 1024;
+constexpr int kSlabs = 1;                    // slabs of 16 weight rows per warp
 constexpr int kWarpRows = 16 * kSlabs;
 constexpr size_t kMmaSharedLimit = 200 * 1024;
 constexpr size_t kMmaSharedFloor = 116 * 1024;   // more than half an SM's shared memory: one CTA per SM
@@ -343,19 +344,23 @@ struct MmaPlan {
   bool ok;
 };
 
-// Measured on B200 against the tensor-core tiles (CUDA graph over weight copies larger than L2,
-// bf16, microseconds, this kernel / tcgen05):
+// Measured on B200 against the other kernels (CUDA graph over weight copies larger than L2, bf16,
+// microseconds, this kernel / tcgen05 tiles; for 1-4 tokens this kernel / look-up tables):
 //                      4096->14336   14336->4096   4096->11008   2048->5632   768->3072
-//    5 tokens           13.3 / 31.5   17.0 / 27.0   11.0 / 23.3    6.6 / 14.7   6.2 / 12.1
-//   16 tokens           16.7 / 29.6   20.7 / 27.3   13.9 / 23.7    8.6 / 15.3   8.0 / 12.8
-//   32 tokens           24.7 / 30.4   31.8 / 27.6   20.7 / 24.7   12.7 / 15.4  11.8 / 13.1
+//    1 token            12.0 /  9.4   14.9 / 11.7   10.4 /  7.4    5.4 /  4.8   4.9 / 4.1
+//    2 tokens           12.1 / 11.6   15.1 / 14.7   10.5 /  9.5    5.4 /  5.7   5.0 / 4.5
+//    4 tokens           12.5 / 21.7   15.2 / 27.7   10.9 / 17.6    5.5 /  8.1   5.0 / 5.9
+//    5 tokens           12.7 / 31.5   15.4 / 27.0   11.0 / 23.3    5.8 / 14.7   5.0 / 12.1
+//   16 tokens           15.1 / 29.6   18.1 / 27.3   12.9 / 23.7    6.4 / 15.3   5.9 / 12.8
+//   32 tokens           21.9 / 30.4   31.8 / 27.6   18.9 / 24.7    9.3 / 15.4   8.5 / 13.1
 //   64 tokens           57.2 / 31.6       - / 27.9  51.6 / 25.6   20.1 / 16.4  19.2 / 13.3
-// hence: up to 32 tokens, 17-32 only for contractions up to 12288 columns.  Four slices were the
-// fastest cut up to 11008 columns (two: 8-15 % slower, one: 50-80 %), eight at 14336.
+// (the rows for 64 tokens and 32 tokens at 14336 columns with two slabs per warp).  Hence: 3 to 32
+// tokens, 17-32 only for contractions up to 12288 columns.  Four slices were the fastest cut up to
+// 11008 columns (two: 8-15 % slower, one: 50-80 %), eight at 14336.
 MmaPlan mma_plan(int64_t samples, int64_t rows, int64_t columns, int dtype) {
   MmaPlan plan = {};
   plan.ok = false;
-  if (samples < 5 || samples > 32 || rows < 1 || columns < 128 || columns % 128 != 0) return plan;
+  if (samples <= lut_max_tokens() || samples > 32 || rows < 1 || columns < 128 || columns % 128 != 0) return plan;
   if (samples > 16 && columns > 12288) return plan;
   plan.tiles = samples <= 8 ? 1 : (samples <= 16 ? 2 : 4);
   const int token_rows = (plan.tiles < 2 ? 2 : plan.tiles) * 8;

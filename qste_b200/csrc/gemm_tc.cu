@@ -192,6 +192,32 @@ __device__ __forceinline__ bool drain_tile(const TcParams& p, const DrainContext
   const int rows_before = c.rank * kTileRows;  // rows of the tile that belong to the other CTA of a pair
   const long long i_tile = (long long)(tile / p.tiles_j) * kItemRows + rows_before, j0 = (long long)tile_j * kBN;
   const int acc = kTall ? 0 : (lt & 1);
+  // The per-row terms of this lane's row (two rows with 256-row tiles) and the sign word of its first
+  // unit are requested BEFORE the wait for the accumulators, and each further sign word one unit
+  // ahead: a unit that asked for them where it uses them waited a trip to L2 per 32 columns, which is
+  // what bounded products with a short contraction (coordinate evidence of a small batch: one
+  // k-block per tile, all epilogue).
+  const long long i_first = i_tile + lane_quarter * 32 + lane, i_second = i_first + kBM;
+  const bool first_ok = i_first < p.I, second_ok = kTileRows > kBM && i_second < p.I;
+  const float add_first = (p.row_add && first_ok) ? __ldg(p.row_add + i_first) : 0.0f;
+  const float add_second = (p.row_add && second_ok) ? __ldg(p.row_add + i_second) : 0.0f;
+  const float mul_first = (p.row_scale && first_ok) ? __ldg(p.row_scale + i_first) : 1.0f;
+  const float mul_second = (p.row_scale && second_ok) ? __ldg(p.row_scale + i_second) : 1.0f;
+  const bool word_loads = (p.inner_pitch & 3) == 0 && (reinterpret_cast<uintptr_t>(p.inner_bits) & 3) == 0;
+  auto sign_word_of = [&](int unit) -> uint32_t {
+    if (!p.inner_bits || item.slot >= 0 || unit >= kUnits) return 0u;
+    const int half = unit / (kBN / 32), chunk = unit % (kBN / 32);
+    const long long i = i_tile + half * kBM + lane_quarter * 32 + lane, j = j0 + chunk * 32;
+    if (i >= p.I || j >= p.J) return 0u;
+    const uint8_t* source = p.inner_bits + i * p.inner_pitch + (j >> 3);
+    if (word_loads && j + 32 <= p.J) return __ldg(reinterpret_cast<const uint32_t*>(source));
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+      if (j + 8 * b < p.J) word |= (uint32_t)source[b] << (8 * b);
+    return word;
+  };
+  uint32_t sign_ahead = sign_word_of(member);
   PROF_BEGIN();
   bool ready = mbar_wait<kIsPair>(c.accum_full + 8u * acc, kTall ? (lt & 1) : ((lt >> 1) & 1), c.abort_flag,
                                   p.diagnostics, __LINE__);
@@ -206,8 +232,10 @@ __device__ __forceinline__ bool drain_tile(const TcParams& p, const DrainContext
     const int half = unit / (kBN / 32), chunk = unit % (kBN / 32);
     const long long i = i_tile + half * kBM + lane_quarter * 32 + lane;
     const bool row_ok = i < p.I;
-    const float add = (p.row_add && row_ok) ? p.row_add[i] : 0.0f;
-    const float row_mul = (p.row_scale && row_ok) ? p.row_scale[i] : 1.0f;
+    const float add = half == 0 ? add_first : add_second;
+    const float row_mul = half == 0 ? mul_first : mul_second;
+    const uint32_t sign_word = sign_ahead;
+    sign_ahead = sign_word_of(unit + kMembers);
     const uint32_t tmem_half = c.tmem_base + ((uint32_t)(lane_quarter * 32) << 16) +
                                (uint32_t)((kTall ? half : acc) * kBN);
     const int column = chunk * 32;
@@ -251,13 +279,6 @@ __device__ __forceinline__ bool drain_tile(const TcParams& p, const DrainContext
       continue;
     }
     PROF_BEGIN();
-    uint32_t sign_word = 0;
-    if (p.inner_bits && row_ok) {
-      const uint8_t* source = p.inner_bits + i * p.inner_pitch + (j >> 3);
-#pragma unroll
-      for (int b = 0; b < 4; ++b)
-        if (j + 8 * b < p.J) sign_word |= (uint32_t)source[b] << (8 * b);
-    }
     if (has_affine) {
 #pragma unroll
       for (int e = 0; e < 32; ++e)

@@ -44,7 +44,7 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
   cudaStream_t s = as_stream(stream);
   const int64_t pitch = (columns + 7) / 8;
 
-  // 1..4 tokens: the look-up-table kernel (gemm_lut.cu: bits streamed once, a thread per weight row,
+  // 1..2 tokens (1..4 of fp32): the look-up-table kernel (gemm_lut.cu: bits streamed once, a thread per weight row,
   // the contraction cut over a thread-block cluster); shapes it does not take fall to the older
   // streaming kernel below, larger batches to the tensor-core tiles
   if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) &&
@@ -52,7 +52,7 @@ int qste_b200_packed_linear_affine(const void* inputs, int dtype, int64_t sample
     note_forward_kernel("lut");
     return lut_forward(inputs, dtype, samples, packed, scale, bias, rows, columns, out, s);
   }
-  // 5..32 tokens of a 16-bit type: weights expanded in registers, warp-level MMAs (gemm_mma.cu)
+  // 3..32 tokens of a 16-bit type: weights expanded in registers, warp-level MMAs (gemm_mma.cu)
   if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) &&
       mma_supported(samples, rows, columns, dtype, inputs, packed, out, out_dtype)) {
     note_forward_kernel("mma");

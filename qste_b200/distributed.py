@@ -9,9 +9,9 @@ whenever a process group exists.  After the reduction every rank runs the same
 deterministic update (the rounding stream depends only on seed, step and index)
 and holds byte-identical coordinates, so nothing else needs to be exchanged.
 
-``mean_evidence(overlap=True)`` runs the NCCL all-reduce, the division by the world
-size and -- when the caller is ``QSTEOptimizer`` -- the coordinate update of that
-surface on a side stream, so that the rest of backward on the compute stream waits
+``mean_evidence(overlap=True)`` runs the NCCL all-reduce (the mean rides the collective
+for power-of-two worlds) and -- when the caller is ``QSTEOptimizer`` -- the coordinate
+update of that surface on a side stream, so that the rest of backward on the compute stream waits
 for none of them; ``QSTEOptimizer.step()`` joins the side stream.  Called by
 anything else the reducer makes the compute stream wait for the reduced tensor
 (``join=True``), which is always safe.
@@ -50,7 +50,7 @@ def _all_reduce(evidence: Tensor, group, average: bool, overlap: bool, join: boo
     world = torch.distributed.get_world_size(group)
     if overlap and evidence.is_cuda:
         # The evidence GEMM that produced `evidence` ran on the current stream.  The
-        # collective (and the division) go to the side stream, after that GEMM.  With
+        # collective goes to the side stream, after that GEMM.  With
         # `join` the compute stream then waits for the result; without it the result is
         # valid on the side stream only and the caller carries on there.
         compute = torch.cuda.current_stream(evidence.device)

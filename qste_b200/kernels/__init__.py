@@ -150,8 +150,8 @@ def first_wait_timeout(device=None) -> dict | None:
 
 
 def last_forward_kernel() -> str:
-    """The kernel family this thread's last ``packed_linear_affine`` ran: ``"lut"`` (1-4 tokens),
-    ``"mma"`` (5-32 tokens of a 16-bit type), ``"stream"``, ``"tensor"`` (tcgen05) or ``"simt"``."""
+    """The kernel family this thread's last ``packed_linear_affine`` ran: ``"lut"`` (1-2 tokens),
+    ``"mma"`` (3-32 tokens of a 16-bit type), ``"stream"``, ``"tensor"`` (tcgen05) or ``"simt"``."""
 
     return _cabi.load().qste_b200_last_forward_kernel().decode()
 

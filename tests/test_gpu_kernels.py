@@ -229,24 +229,26 @@ def test_look_up_table_forward_for_one_to_four_tokens(samples, rows, columns, dt
     not divide over the clusters, contractions of one unit of 128 columns up to 16384 (four and
     eight slices), with and without bias."""
 
-    if samples > 2 and columns == 16384:
+    if samples > 2 and columns == 16384 and dtype == torch.float32:
         pytest.skip("four tables of a 2048-column slice do not fit; the shape falls to other kernels")
     x, _, bits, scale, bias = _problem(samples, rows, columns, dtype, seed=samples + rows)
     with forced_path("stream"):
         y = kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
         y_nobias = kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), None, columns)
     assert y.dtype == dtype and y.shape == (samples, rows)
+    # 16-bit batches of three and four are handed on to the register-expansion kernel
+    assert kernels.last_forward_kernel() == ("lut" if samples <= 2 or dtype == torch.float32 else "mma")
     bar = 1e-5 if dtype == torch.float32 else 1e-3
     want = oracle.packed_linear_affine(x.float(), bits, scale, bias, columns)
     assert rel(host(y), like(want, dtype)) <= bar
     assert rel(host(y_nobias), like(oracle.packed_linear_affine(x.float(), bits, scale, None, columns), dtype)) <= bar
 
 
-@pytest.mark.parametrize("samples", [5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("samples", [3, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (4104, 2048), (300, 12288),
                                           (14336, 4096), (4096, 14336), (11008, 4096), (5632, 2048)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_register_expansion_forward_for_5_to_32_tokens(samples, rows, columns, dtype):
+def test_register_expansion_forward_for_3_to_32_tokens(samples, rows, columns, dtype):
     """The warp-MMA kernel of gemm_mma.cu against the oracle: every count of token tiles (1, 2, 4)
     at its first and last batch size, row counts that do not divide over the clusters or the 16-row
     slabs, contractions from one unit of 128 columns (one CTA per cluster) to 14336 (eight), runs of
@@ -273,11 +275,11 @@ def test_small_batch_forward_dispatch():
 
     rows, columns = 4096, 4096
     chosen = {}
-    for samples in (1, 4, 5, 32, 33, 128):
+    for samples in (1, 2, 3, 32, 33, 128):
         x, _, bits, scale, bias = _problem(samples, rows, columns, torch.bfloat16, seed=samples)
         kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
         chosen[samples] = kernels.last_forward_kernel()
-    assert chosen == {1: "lut", 4: "lut", 5: "mma", 32: "mma", 33: "tensor", 128: "tensor"}
+    assert chosen == {1: "lut", 2: "lut", 3: "mma", 32: "mma", 33: "tensor", 128: "tensor"}
     x, _, bits, scale, bias = _problem(16, rows, columns, torch.float32, seed=3)
     kernels.packed_linear_affine(x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE), columns)
     assert kernels.last_forward_kernel() == "tensor"      # fp32 activations: three bf16 planes on tcgen05

@@ -394,3 +394,84 @@ def test_the_allocation_free_update_refuses_what_it_cannot_copy():
     arguments["gradient"] = torch.zeros(16, 6).t()
     with pytest.raises(RuntimeError, match="must be contiguous"):
         kernels.coordinate_update_static(*arguments.values(), flips=torch.zeros((), dtype=torch.int64), **options)
+
+
+# -- the overlap plumbing of the evidence exchange, on fakes ------------------------------------
+
+
+class _RecordingStream:
+    def __init__(self):
+        self.calls = []
+
+    def wait_event(self, event):
+        self.calls.append(("event", event))
+
+    def wait_stream(self, stream):
+        self.calls.append(("stream", stream))
+
+
+def test_side_stream_waits_for_the_evidence_event_when_there_is_one():
+    """The fused backward tags the evidence with the event recorded after the evidence product;
+    the side stream must wait for that event alone, and for the whole compute stream otherwise."""
+
+    from qste_b200.distributed import wait_for_producer
+
+    side, compute = _RecordingStream(), _RecordingStream()
+    tagged = torch.zeros(4)
+    tagged._qste_ready = "evidence-done"
+    wait_for_producer(side, compute, tagged)
+    assert side.calls == [("event", "evidence-done")]
+    side.calls.clear()
+    wait_for_producer(side, compute, torch.zeros(4))
+    assert side.calls == [("stream", compute)]
+
+
+def test_backward_reserve_setting(monkeypatch):
+    """The reserve is a setting of the backward GEMMs only: the setter returns the previous value,
+    never goes negative, and the overlapped reducer's default is 8 unless the environment says
+    otherwise."""
+
+    from qste_b200 import distributed, kernels
+
+    first = kernels.set_backward_reserve(5)
+    try:
+        assert kernels.set_backward_reserve(-3) == 5
+        assert kernels.set_backward_reserve(0) == 0
+        monkeypatch.delenv("QSTE_B200_RESERVED_SMS", raising=False)
+        distributed._reserve_for_overlap(None)
+        assert kernels.set_backward_reserve(0) == 8
+        monkeypatch.setenv("QSTE_B200_RESERVED_SMS", "12")
+        distributed._reserve_for_overlap(None)
+        assert kernels.set_backward_reserve(0) == 12
+        distributed._reserve_for_overlap(4)
+        assert kernels.set_backward_reserve(0) == 4
+    finally:
+        kernels.set_backward_reserve(first)
+
+
+def test_reserved_sms_of_the_library_are_per_thread():
+    """qste_b200_set_reserved_sms changes the calling thread's GEMM grids only (the side stream's
+    host thread must not shrink the forward of another)."""
+
+    import os
+    import threading
+
+    from qste_b200.kernels import _cabi
+
+    library = _cabi.load()
+    before = library.qste_b200_set_reserved_sms(6)
+    seen = {}
+
+    def other():
+        seen["initial"] = library.qste_b200_set_reserved_sms(3)
+        seen["own"] = library.qste_b200_set_reserved_sms(0)
+
+    worker = threading.Thread(target=other)
+    worker.start()
+    worker.join()
+    try:
+        # the other thread started from the environment's value (0 when unset), not from this thread's 6
+        assert seen["initial"] == max(0, int(os.environ.get("QSTE_B200_RESERVED_SMS", "0"))) and seen["own"] == 3
+        assert library.qste_b200_set_reserved_sms(before) == 6     # untouched by the other thread
+    finally:
+        library.qste_b200_set_reserved_sms(before)
