@@ -64,6 +64,14 @@ bool mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, co
 int mma_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed, const float* scale,
                 const float* bias, int64_t rows, int64_t columns, void* out, cudaStream_t stream);
 
+// Coordinate evidence (with g_scale and g_bias) for 1..32 samples in one kernel on the CUDA cores,
+// bound by writing the result (evidence_lut.cu).  aux = [offset (M), act_scale (M)].
+bool evidence_lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* grad,
+                            const float* evidence);
+int evidence_lut(const void* grad, int dtype, int64_t samples, int64_t rows, const uint8_t* act_bits, const float* aux,
+                 int64_t columns, const uint8_t* weight_bits, const float* weight_scale, float* evidence, float* g_scale,
+                 float* g_bias, cudaStream_t stream);
+
 int simt_gemm(const void* A, int a_dtype, int64_t stride_ai, int64_t stride_ak, const uint8_t* bits,
               int64_t bit_pitch, int bits_row_is_k, const float* cs, const float* os,
               const float* ob, void* C, int c_dtype, int64_t I, int64_t J, int64_t K,

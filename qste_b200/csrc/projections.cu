@@ -184,6 +184,11 @@ int qste_b200_linear_backward_evidence(const void* grad, int dtype, int64_t samp
   if (!evidence && columns > 0) return QSTE_ERR_NULL;
   if (!weight_scale || (columns > 0 && !weight_bits)) return QSTE_ERR_NULL;
   if (samples > 0 && (!grad || !aux || (columns > 0 && !act_bits))) return QSTE_ERR_NULL;
+  // 1..32 samples: one kernel on the CUDA cores, bound by writing the result (evidence_lut.cu)
+  if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) && samples > 0 && columns > 0 &&
+      evidence_lut_supported(samples, rows, columns, dtype, grad, evidence))
+    return evidence_lut(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
+                        g_scale, g_bias, as_stream(stream));
   if (path == QSTE_PATH_STREAM) return QSTE_ERR_UNSUPPORTED;
   const size_t need = qste_b200_linear_backward_evidence_workspace(samples, rows, columns, dtype, path);
   if (!workspace || workspace_bytes < need) return QSTE_ERR_WORKSPACE;
@@ -294,7 +299,10 @@ int qste_b200_linear_backward_staged(const void* grad, int dtype, int64_t sample
   if (!workspace || workspace_bytes < qste_b200_linear_backward_workspace(samples, rows, columns, dtype))
     return QSTE_ERR_WORKSPACE;
   if (!aligned(workspace, 256)) return QSTE_ERR_ALIGNMENT;
-  const bool fused = dtype == QSTE_BF16 && samples > 0 && rows > 0 && columns > 0 && grad && weight_bits &&
+  // (a batch of up to 32 samples takes the two separate calls: its evidence has a kernel of its own)
+  const bool small = small_batch_auto() && samples > 0 && columns > 0 && grad && evidence &&
+                     evidence_lut_supported(samples, rows, columns, dtype, grad, evidence);
+  const bool fused = !small && dtype == QSTE_BF16 && samples > 0 && rows > 0 && columns > 0 && grad && weight_bits &&
                      weight_scale && act_bits && aux && grad_input && evidence &&
                      tc_supported(TC_TRANSPOSE, samples, columns, rows, dtype, grad, weight_bits, grad_input, grad_input_dtype) &&
                      tc_supported(TC_EVIDENCE, rows, columns, samples, dtype, grad, act_bits, evidence, QSTE_F32);

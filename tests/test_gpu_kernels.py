@@ -360,6 +360,36 @@ def test_tensor_core_evidence(samples, rows, columns, dtype):
     assert kernels.wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("samples", [1, 3, 4, 5, 16, 17, 32])
+@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (300, 16384), (4104, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_small_batch_evidence_kernel(samples, rows, columns, dtype):
+    """evidence_lut.cu against the oracle: evidence, row-scale gradient and bias gradient of batches
+    of 1..32 samples in one launch -- every count of four-sample groups at its edges, row counts
+    that do not divide over the warps, contractions from 128 to 16384 columns.  "stream" forces the
+    kernel (the call fails where it does not apply)."""
+
+    x, dy, bits, scale, _ = _problem(samples, rows, columns, dtype, seed=samples + columns)
+    act_bits, act_offset, act_scale = kernels.pack_affine_rows(x.to(DEVICE))
+    aux = torch.stack((act_offset, act_scale))
+    with forced_path("stream"):
+        evidence, g_scale, g_bias = kernels.linear_backward_evidence(
+            dy.to(DEVICE), act_bits, aux, columns, bits.to(DEVICE), scale.to(DEVICE), want_bias=True)
+        _, g_scale_only, none = kernels.linear_backward_evidence(
+            dy.to(DEVICE), act_bits, aux, columns, bits.to(DEVICE), scale.to(DEVICE))
+    assert none is None and torch.equal(g_scale, g_scale_only)
+    grad = dy.float().contiguous()
+    plain = oracle.evidence_from_packed(grad, host(act_bits), columns, host(act_scale))
+    decoded = plain.astype(np.float64) + (grad.double().t().numpy() @ host(act_offset).astype(np.float64))[:, None]
+    assert rel(host(evidence), decoded * scale.double().numpy()[:, None]) <= 1e-5
+    assert rel(host(g_scale), oracle.packed_row_inner(decoded.astype(np.float32), bits, columns)) <= 1e-4
+    assert rel(host(g_bias), dy.double().sum(0).numpy()) <= 1e-5
+    # the dispatcher's own choice is the same kernel: identical bits
+    auto, auto_scale, _ = kernels.linear_backward_evidence(
+        dy.to(DEVICE), act_bits, aux, columns, bits.to(DEVICE), scale.to(DEVICE), want_bias=True)
+    assert torch.equal(auto, evidence) and torch.equal(auto_scale, g_scale)
+
+
 def test_whole_backward_with_rows_of_very_different_magnitude():
     """The fused backward scales every row of the gradient by its own power of two before the
     fp16 re-encoding: rows 2^40 apart must each come back with their own relative accuracy (dX)
