@@ -500,6 +500,16 @@ def kernel_breakdown(device, tokens: int) -> dict:
     x1, bits1, scale1 = _gemm_inputs(device, 1, k, n, seed=4)
     stream("forward_m1_stream", lambda: kernels.packed_linear_affine(x1, bits1, scale1, None, k),
            n * k / 8 + 4 * n + 2 * k + 2 * n, repeat=20, replay=True)
+    # 16 tokens: the register-expansion forward and the one-launch evidence (bits and result from L2
+    # where they fit; `gemm_sweep` times the same calls over weight copies larger than L2)
+    x16, bits16, scale16 = _gemm_inputs(device, 16, k, n, seed=5)
+    stream("forward_m16_registers", lambda: kernels.packed_linear_affine(x16, bits16, scale16, None, k),
+           n * k / 8 + 8 * n + 16 * (2 * k + 2 * n), repeat=20, replay=True)
+    dy16 = torch.randn(16, n, device=device, dtype=torch.bfloat16, generator=generator)
+    act16, offset16, ascale16 = kernels.pack_affine_rows(x16)
+    aux16 = torch.stack((offset16, ascale16))
+    stream("evidence_m16_tables", lambda: kernels.linear_backward_evidence(dy16, act16, aux16, k, bits16, scale16),
+           4.0 * n * k + n * k / 8 + 16 * k / 8 + 2 * 16 * n + 12 * n, repeat=10)
     return out
 
 

@@ -34,7 +34,13 @@ template <typename T> __device__ __forceinline__ float round_through(float v) {
   return DType<T>::load(&stored);
 }
 
-__device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+// 1 / (1 + e^-x).  For a 16-bit tensor the fast exponential and division are exact to well inside
+// the type's last bit (2^-21 relative against 2^-9 / 2^-11) and take a third of the instructions.
+template <typename T>
+__device__ __forceinline__ float sigmoidf(float x) {
+  if (sizeof(T) == 2) return __fdividef(1.0f, 1.0f + __expf(-x));
+  return 1.0f / (1.0f + expf(-x));
+}
 
 // y = f(x) and d = f'(x).  Where the reference forms the derivative from the activation's
 // OUTPUT (tanh, sigmoid, elu, celu, selu: nn.py:414-470) it uses the output as stored, i.e.
@@ -51,7 +57,7 @@ __device__ __forceinline__ void activate(float x, float a, float& y, float& d) {
     y = 0.5f * x * (1.0f + t);
     d = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * c * (1.0f + 3.0f * k * x * x);
   } else if (kKind == ACT_SILU) {
-    const float s = sigmoidf(x);
+    const float s = sigmoidf<T>(x);
     y = x * s;
     d = s * (1.0f + x * (1.0f - s));
   } else if (kKind == ACT_TANH) {
@@ -59,7 +65,7 @@ __device__ __forceinline__ void activate(float x, float a, float& y, float& d) {
     const float stored = round_through<T>(y);
     d = 1.0f - stored * stored;
   } else if (kKind == ACT_SIGMOID) {
-    y = sigmoidf(x);
+    y = sigmoidf<T>(x);
     const float stored = round_through<T>(y);
     d = stored * (1.0f - stored);
   } else if (kKind == ACT_ELU) {
@@ -73,12 +79,12 @@ __device__ __forceinline__ void activate(float x, float a, float& y, float& d) {
     d = x > 0.0f ? kSeluScale : round_through<T>(y) + kSeluScale * kSeluAlpha;
   } else if (kKind == ACT_SOFTPLUS) {
     y = x * a > 20.0f ? x : log1pf(expf(x * a)) / a;
-    d = sigmoidf(a * x);
+    d = sigmoidf<T>(a * x);
   } else if (kKind == ACT_MISH) {
     const float softplus = x > 20.0f ? x : log1pf(expf(x));
     const float t = tanhf(softplus);
     y = x * t;
-    d = t + x * (1.0f - t * t) * sigmoidf(x);
+    d = t + x * (1.0f - t * t) * sigmoidf<T>(x);
   } else {  // ACT_HARDSWISH
     y = x * fminf(fmaxf(x + 3.0f, 0.0f), 6.0f) * (1.0f / 6.0f);
     d = x <= -3.0f ? 0.0f : (x >= 3.0f ? 1.0f : (2.0f * x + 3.0f) * (1.0f / 6.0f));
@@ -123,6 +129,9 @@ smooth_forward_kernel(const T* __restrict__ x, long long rows, long long columns
     for (int w = 1; w < kActThreads / 32; ++w) largest = fmaxf(largest, warp_max[w]);
     const float step = fmaxf(largest, 1e-8f) / 127.0f;
     if (threadIdx.x == 0) scale[row] = step;
+    // one reciprocal per row instead of a division per element: the quotient moves by an ulp, the
+    // int8 value only where it sat within that of a half
+    const float inverse = 1.0f / step;
     int8_t* tape = q + row * columns;
     // each thread quantises what it wrote itself: no barrier needed before, one after (the
     // next row reuses the buffer and warp_max)
@@ -130,7 +139,7 @@ smooth_forward_kernel(const T* __restrict__ x, long long rows, long long columns
       int8_t packed[kVec];
 #pragma unroll
       for (int e = 0; e < kVec; ++e)
-        packed[e] = (int8_t)fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(derivative[c + e], step))));
+        packed[e] = (int8_t)fminf(127.0f, fmaxf(-127.0f, rintf(derivative[c + e] * inverse)));
       if (kVec == 8) *reinterpret_cast<uint2*>(tape + c) = *reinterpret_cast<const uint2*>(packed);
       else if (kVec == 4) *reinterpret_cast<uint32_t*>(tape + c) = *reinterpret_cast<const uint32_t*>(packed);
       else tape[c] = packed[0];
