@@ -1048,10 +1048,6 @@ TcPlan tc_plan(long long I, long long J, int kblocks_total) {
   const long long rest = tiles % workers;
   if (!never_split && rest > 0) {
     long long slices = workers / rest;
-    // QSTE_B200_TC_SLICES=n: n times as many slices (A/B timing: with the device-side queue a worker can
-    // take several short slices)
-    static const int finer = getenv("QSTE_B200_TC_SLICES") ? atoi(getenv("QSTE_B200_TC_SLICES")) : 0;
-    if (finer > 1) slices = (workers * finer) / rest;
     const int shortest = plan.mode == kModeShort ? 4 : 8;
     if (slices > kblocks_total / shortest) slices = kblocks_total / shortest;
     if (slices >= 2) {
