@@ -21,9 +21,9 @@
 //     of the small-batch forward, with the samples as the contraction) -- 16 words per group, so
 //     lanes looking up the same group never conflict;
 //   * each lane then walks four consecutive columns at a time: one 16-byte load of their four
-//     patterns, one look-up and add per group, the offset term, the product with the weight's
-//     sign for g_scale, the row scale, and one 16-byte store -- a warp stores 512 contiguous
-//     bytes per step;
+//     patterns, one look-up and add per group (the offset term rides the first group's entries),
+//     the product with the weight's sign for g_scale, the row scale, and one 16-byte store -- a
+//     warp stores 512 contiguous bytes per step;
 //   * g_bias, the offset term and g_scale are warp sums of one value per lane.
 //
 // Everything is fp32 from the 16-bit gradient on (no re-encoding), no workspace, no atomics.
@@ -119,8 +119,9 @@ evidence_lut_kernel(const __grid_constant__ EvidenceParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int pt = first + e;
+          // (the offset term rides the first group's entries: one add per coordinate less)
           table[g * 16 + pt] = ((pt & 1) ? v[0] : -v[0]) + ((pt & 2) ? v[1] : -v[1]) + ((pt & 4) ? v[2] : -v[2]) +
-                               ((pt & 8) ? v[3] : -v[3]);
+                               ((pt & 8) ? v[3] : -v[3]) + (g == 0 ? add : 0.0f);
         }
       }
     }
@@ -131,7 +132,8 @@ evidence_lut_kernel(const __grid_constant__ EvidenceParams p) {
     const uint32_t table_base = (uint32_t)__cvta_generic_to_shared(table);
     float inner = 0.0f;
     // -- four consecutive columns per lane and step, 128 per warp
-    for (long long k0 = 4 * lane; k0 < p.K; k0 += 128) {
+    const int columns = (int)p.K;
+    for (int k0 = 4 * lane; k0 < columns; k0 += 128) {
       const uint4 words = *reinterpret_cast<const uint4*>(pattern + k0);
       // bits 0..3: where the weight's sign of the four columns is MINUS
       const uint32_t minus = ~((uint32_t)weight_row[k0 >> 3] >> (k0 & 4));
@@ -139,8 +141,7 @@ evidence_lut_kernel(const __grid_constant__ EvidenceParams p) {
       float out[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float sum = add_lookups<0, kGroups>(0.0f, word[e], table_base);
-        const float v = sum + add;
+        const float v = add_lookups<0, kGroups>(0.0f, word[e], table_base);
         // v with its sign flipped where the weight's sign is minus
         inner += __uint_as_float(__float_as_uint(v) ^ ((minus << (31 - e)) & 0x80000000u));
         out[e] = v * row_scale;

@@ -187,11 +187,12 @@ constexpr size_t kLutSharedFloor = 116 * 1024;   // more than half an SM's share
 template <typename T, int kM>
 int lut_cluster_capacity(int cluster_size) {
   auto kernel = packed_lut_forward_kernel<T, kM>;
-  static int cached[64][4] = {};
+  static int cached[64][9] = {};
   int device = 0;
   cudaGetDevice(&device);
+  if (cluster_size < 1 || cluster_size > 8) return 0;
   const bool slot = device >= 0 && device < 64;
-  const int index = cluster_size <= 1 ? 0 : (cluster_size == 2 ? 1 : (cluster_size == 4 ? 2 : 3));
+  const int index = cluster_size;
   if (slot && cached[device][index] > 0) return cached[device][index];
   const int by_count = sm_count() / cluster_size > 0 ? sm_count() / cluster_size : 1;
   int clusters = 0;
@@ -210,10 +211,9 @@ int lut_cluster_capacity(int cluster_size) {
     if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) clusters = 0;
   }
   cudaGetLastError();
-  if (clusters <= 0) clusters = by_count * 3 / 4 > 0 ? by_count * 3 / 4 : 1;
   if (clusters > by_count) clusters = by_count;
-  if (slot) cached[device][index] = clusters;
-  return clusters;
+  if (slot && clusters > 0) cached[device][index] = clusters;
+  return clusters;    // 0: the driver cannot place such a cluster, the kernel does not apply
 }
 
 int lut_cluster_capacity(int dtype, int tokens, int cluster_size) {
@@ -283,7 +283,7 @@ LutPlan lut_plan(int64_t samples, int64_t rows, int64_t columns, int dtype) {
     const int table_units = (widest + kLutChunk - 1) / kLutChunk * kLutChunk;
     const size_t table_bytes = (size_t)plan.tokens * table_units * 32 * 16 * sizeof(float);
     int clusters = lut_cluster_capacity(dtype, plan.tokens, s);   // resident at once, a CTA per SM
-    if (clusters < 1) clusters = 1;
+    if (clusters < 1) continue;
     int group_rows = (int)ceil_div(rows, clusters);
     clusters = (int)ceil_div(rows, group_rows);
     const size_t partial_bytes = (size_t)plan.tokens * group_rows * sizeof(float);

@@ -288,11 +288,11 @@ int mma_cluster_capacity(int cluster_size) {
   int clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
     cudaGetLastError();
-    clusters = 0;
+    return 0;          // the driver cannot place such a cluster: this kernel does not apply
   }
   const int by_count = sm_count() / cluster_size;
-  if (clusters <= 0 || clusters > by_count) clusters = clusters <= 0 ? (by_count * 3 / 4 > 0 ? by_count * 3 / 4 : 1) : by_count;
-  if (slot) cached[device][index] = clusters;
+  if (clusters > by_count) clusters = by_count;
+  if (slot && clusters > 0) cached[device][index] = clusters;
   return clusters;
 }
 

@@ -222,7 +222,7 @@ def test_small_batch_streaming_forward(samples, rows, columns, dtype):
 
 
 @pytest.mark.parametrize("samples", [1, 2, 3, 4])
-@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (4104, 2048), (300, 16384), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (33, 384), (515, 1024), (3072, 768), (4104, 2048), (300, 16384), (14336, 4096), (4096, 14336)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_look_up_table_forward_for_one_to_four_tokens(samples, rows, columns, dtype):
     """The cluster kernel of gemm_lut.cu against the oracle: every token count, row counts that do
@@ -245,7 +245,7 @@ def test_look_up_table_forward_for_one_to_four_tokens(samples, rows, columns, dt
 
 
 @pytest.mark.parametrize("samples", [3, 8, 9, 16, 17, 32])
-@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (4104, 2048), (300, 12288),
+@pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (33, 384), (515, 1024), (3072, 768), (4104, 2048), (300, 12288),
                                           (14336, 4096), (4096, 14336), (11008, 4096), (5632, 2048)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_register_expansion_forward_for_3_to_32_tokens(samples, rows, columns, dtype):
