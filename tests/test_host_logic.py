@@ -341,6 +341,22 @@ def test_retained_bytes_per_sample_are_one_bit_plus_two_floats(cpu_kernels):
     assert per_sample == 1024 / 8 + 8
 
 
+def test_forward_without_grad_keeps_no_activation_bits(cpu_kernels, monkeypatch):
+    """Evaluation through a trainable module: with autograd off nothing is packed or saved, and
+    the output is the training forward's."""
+
+    model, layer = _one_layer(rows=32, columns=256)
+    packs = []
+    original = kernels.pack_affine_rows
+    monkeypatch.setattr(kernels, "pack_affine_rows", lambda values: (packs.append(values.shape), original(values))[1])
+    x = torch.randn(5, 256, generator=torch.Generator().manual_seed(1))
+    trained = model(x)
+    assert len(packs) == 1
+    with torch.no_grad():
+        evaluated = model(x)
+    assert len(packs) == 1 and torch.equal(evaluated, trained.detach())
+
+
 def test_product_kernels_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="CUDA tensor"):
         kernels.pack_coordinate(torch.zeros(4, 8, dtype=torch.int8))
