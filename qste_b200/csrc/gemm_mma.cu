@@ -91,8 +91,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) 
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
 }
 
-// Bits `pair` and `pair` + 16 of `word` (pair < 16, a constant after unrolling) as a pair of 16-bit values, -1 where the bit is clear and +1
-// where it is set: the shift puts them on the sign bits of the two halves.
+// Bits `pair` and `pair` + 16 of `word` (pair < 16, a constant after unrolling) as a pair of
+// 16-bit values, -1 where the bit is clear and +1 where it is set: the shift puts them on the sign
+// bits of the two halves.
 template <typename T>
 __device__ __forceinline__ uint32_t sign_pair(uint32_t word, int pair) {
   return MmaType<T>::kMinusOnes ^ ((word << (15 - pair)) & 0x80008000u);
