@@ -285,6 +285,30 @@ def test_small_batch_forward_dispatch():
     assert kernels.last_forward_kernel() == "tensor"      # fp32 activations: three bf16 planes on tcgen05
 
 
+@pytest.mark.parametrize("samples", [1, 8, 32, 128])
+def test_forward_replays_from_a_cuda_graph(samples):
+    """A decode loop replays its launches from a CUDA graph: every forward kernel family must be
+    capturable (no host read, no allocation of its own, no stream of its own) and a replay must
+    return the bits of the eager call."""
+
+    rows, columns = 3072, 768
+    x, _, bits, scale, bias = _problem(samples, rows, columns, torch.bfloat16, seed=samples)
+    x, bits, scale, bias = x.to(DEVICE), bits.to(DEVICE), scale.to(DEVICE), bias.to(DEVICE)
+    eager = kernels.packed_linear_affine(x, bits, scale, bias, columns)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        kernels.packed_linear_affine(x, bits, scale, bias, columns)      # this stream's workspace exists
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            captured = kernels.packed_linear_affine(x, bits, scale, bias, columns)
+        captured.zero_()
+        graph.replay()
+        side.synchronize()
+    assert torch.equal(captured, eager)
+    torch.cuda.current_stream().wait_stream(side)
+
+
 TENSOR_SHAPES = [(128, 256, 128), (200, 300, 256), (1024, 512, 1024), (77, 1000, 384), (4096, 2048, 2048)]
 # Shapes whose output has at least 148 tiles of 256 x 256, ragged on both sides: the kernel then
 # runs its 256-row tiles, two or three per CTA, with the expander warps sharing the epilogue.
