@@ -13,6 +13,7 @@ to the CPU.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 
@@ -72,6 +73,18 @@ def _ptr(tensor: Tensor | None):
             "device; kernels run on the current device's stream."
         )
     return ctypes.c_void_p(tensor.data_ptr())
+
+
+_NO_SWITCH = contextlib.nullcontext()
+
+
+def _on(device: torch.device):
+    """Context that makes `device` current for the calls inside; nothing at all when it already
+    is (the common case, and a device switch costs more host time than a small kernel runs)."""
+
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 def _stream(device: torch.device):
@@ -189,7 +202,7 @@ def _unpack(packed: Tensor, columns: int, dtype: torch.dtype, zero_one: int) -> 
     packed = packed.contiguous()
     rows = packed.shape[0]
     out = torch.empty(rows, int(columns), dtype=dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _on(packed.device):
         _cabi.check(_cabi.load().qste_b200_unpack_rows(
             _ptr(packed), rows, int(columns), _ptr(out), _DTYPES[dtype], zero_one,
             _stream(packed.device)), "unpack_rows")
@@ -205,7 +218,7 @@ def pack_bits(mask: Tensor) -> Tensor:
     mask = mask.contiguous()
     rows, columns = mask.shape
     packed = torch.empty(rows, (columns + 7) // 8, dtype=torch.uint8, device=mask.device)
-    with torch.cuda.device(mask.device):
+    with _on(mask.device):
         _cabi.check(_cabi.load().qste_b200_pack_bits(
             _ptr(mask), rows, columns, _ptr(packed), _stream(mask.device)), "pack_bits")
     return packed
@@ -223,7 +236,7 @@ def apply_bits(values: Tensor, packed: Tensor, columns: int) -> Tensor:
     values = values.contiguous()
     packed = packed.contiguous()
     out = torch.empty_like(values)
-    with torch.cuda.device(values.device):
+    with _on(values.device):
         _cabi.check(_cabi.load().qste_b200_apply_bits(
             _ptr(values), _DTYPES[values.dtype], _ptr(packed), values.shape[0], int(columns),
             _ptr(out), _stream(values.device)), "apply_bits")
@@ -245,7 +258,7 @@ def pack_affine_rows(values: Tensor) -> tuple[Tensor, Tensor, Tensor]:
     packed = torch.empty(rows, (columns + 7) // 8, dtype=torch.uint8, device=device)
     offset = torch.empty(rows, dtype=torch.float32, device=device)
     scale = torch.empty(rows, dtype=torch.float32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         _cabi.check(_cabi.load().qste_b200_pack_affine_rows(
             _ptr(values), _DTYPES[values.dtype], rows, columns, _ptr(packed), _ptr(offset),
             _ptr(scale), _stream(device)), "pack_affine_rows")
@@ -261,7 +274,7 @@ def pack_coordinate(coordinate: Tensor) -> Tensor:
     coordinate = coordinate.contiguous()
     rows, columns = coordinate.shape
     packed = torch.empty(rows, (columns + 7) // 8, dtype=torch.uint8, device=coordinate.device)
-    with torch.cuda.device(coordinate.device):
+    with _on(coordinate.device):
         _cabi.check(_cabi.load().qste_b200_pack_coordinate(
             _ptr(coordinate), rows, columns, _ptr(packed), _stream(coordinate.device)),
             "pack_coordinate")
@@ -296,7 +309,7 @@ def packed_linear_affine(inputs: Tensor, packed: Tensor, scale: Tensor, bias: Te
     code = _DTYPES[inputs.dtype]
     path = _path()
     library = _cabi.load()
-    with torch.cuda.device(device):
+    with _on(device):
         need = library.qste_b200_packed_linear_affine_workspace(samples, rows, columns, code, path)
         workspace = _workspace(device, need)
         _cabi.check(library.qste_b200_packed_linear_affine(
@@ -329,7 +342,7 @@ def packed_transpose(inputs: Tensor, packed: Tensor, columns: int,
     code = _DTYPES[inputs.dtype]
     path = _path()
     library = _cabi.load()
-    with torch.cuda.device(device):
+    with _on(device):
         need = library.qste_b200_packed_transpose_workspace(samples, rows, columns, code, path)
         workspace = _workspace(device, need)
         _cabi.check(library.qste_b200_packed_transpose(
@@ -364,7 +377,7 @@ def evidence_from_packed(grad: Tensor, packed: Tensor, columns: int,
     code = _DTYPES[grad.dtype]
     path = _path()
     library = _cabi.load()
-    with torch.cuda.device(device):
+    with _on(device):
         need = library.qste_b200_evidence_from_packed_workspace(samples, rows, columns, code, path)
         workspace = _workspace(device, need)
         _cabi.check(library.qste_b200_evidence_from_packed(
@@ -410,7 +423,7 @@ def linear_backward_evidence(grad: Tensor, act_bits: Tensor, aux: Tensor, column
     code = _DTYPES[grad.dtype]
     path = _path()
     library = _cabi.load()
-    with torch.cuda.device(device):
+    with _on(device):
         need = library.qste_b200_linear_backward_evidence_workspace(samples, rows, columns, code, path)
         workspace = _workspace(device, need)
         _cabi.check(library.qste_b200_linear_backward_evidence(
@@ -489,7 +502,7 @@ def linear_backward(grad: Tensor, weight_bits: Tensor, weight_scale: Tensor, col
         if not evidence_ready.cuda_event:
             evidence_ready.record()  # torch creates the CUDA event at its first record
         event = ctypes.c_void_p(evidence_ready.cuda_event)
-    with torch.cuda.device(device):
+    with _on(device):
         reserve = _backward_reserve
         if reserve:
             library.qste_b200_set_reserved_sms(reserve)
@@ -518,7 +531,7 @@ def packed_row_inner(matrix: Tensor, packed: Tensor, columns: int) -> Tensor:
     source = source.contiguous()
     packed = packed.contiguous()
     out = torch.empty(source.shape[0], dtype=torch.float32, device=matrix.device)
-    with torch.cuda.device(matrix.device):
+    with _on(matrix.device):
         _cabi.check(_cabi.load().qste_b200_packed_row_inner(
             _ptr(source), _ptr(packed), source.shape[0], columns, _ptr(out),
             _stream(matrix.device)), "packed_row_inner")
@@ -539,7 +552,7 @@ def packed_embedding(ids: Tensor, packed: Tensor, scale: Tensor, columns: int) -
     out_dtype = scale.dtype if scale.dtype in _DTYPES else torch.float32
     out = torch.empty(flat.numel(), columns, dtype=out_dtype, device=device)
     bad = torch.zeros(1, dtype=torch.int32, device=device)
-    with torch.cuda.device(device):
+    with _on(device):
         _cabi.check(_cabi.load().qste_b200_packed_embedding(
             _ptr(flat), flat.numel(), _ptr(packed.contiguous()), _ptr(_f32(scale)), rows, columns,
             _ptr(out), _DTYPES[out_dtype], _ptr(bad), _stream(device)), "packed_embedding")
@@ -577,7 +590,7 @@ def smooth_forward(inputs: Tensor, kind: str, parameter: float = 1.0) -> tuple[T
     outputs = torch.empty_like(flat)
     derivative = torch.empty(rows, columns, dtype=torch.int8, device=flat.device)
     scale = torch.empty(rows, dtype=torch.float32, device=flat.device)
-    with torch.cuda.device(flat.device):
+    with _on(flat.device):
         _cabi.check(_cabi.load().qste_b200_smooth_forward(
             _ptr(flat), code, rows, columns, SMOOTH_KINDS[kind], float(parameter), _ptr(outputs), _ptr(derivative),
             _ptr(scale), _stream(flat.device)), "smooth_forward")
@@ -595,7 +608,7 @@ def smooth_backward(grad: Tensor, derivative: Tensor, scale: Tensor) -> Tensor:
         return smooth_backward(grad.float(), derivative, scale).to(grad.dtype)
     flat = grad.reshape(rows, columns).contiguous()
     out = torch.empty_like(flat)
-    with torch.cuda.device(flat.device):
+    with _on(flat.device):
         _cabi.check(_cabi.load().qste_b200_smooth_backward(
             _ptr(flat), _DTYPES[flat.dtype], _ptr(derivative.contiguous()), _ptr(_f32(scale)), rows, columns, _ptr(out),
             _stream(flat.device)), "smooth_backward")
@@ -672,7 +685,7 @@ def coordinate_update(gradient: Tensor, coordinate: Tensor, packed: Tensor, mome
     gradient = gradient if gradient.is_contiguous() else gradient.contiguous()
     step_tensor = step if torch.is_tensor(step) else None
     library = _cabi.load()
-    with torch.cuda.device(device):
+    with _on(device):
         need = library.qste_b200_coordinate_update_workspace(rows, columns, block_size)
         workspace = _workspace(device, need)
         _cabi.check(library.qste_b200_coordinate_update(
@@ -713,7 +726,7 @@ def coordinate_update_static(gradient: Tensor, coordinate: Tensor, packed: Tenso
         return flips.zero_()
     rows, columns = gradient.shape
     device = gradient.device
-    with torch.cuda.device(device):
+    with _on(device):
         _cabi.check(_cabi.load().qste_b200_coordinate_update_static(
             _ptr(gradient), _ptr(coordinate), _ptr(packed), _ptr(moment_q), _ptr(moment_scale),
             _ptr(row_v), _ptr(col_v), rows, columns, float(beta1), float(beta2), float(update_clip),
