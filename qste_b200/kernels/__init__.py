@@ -54,10 +54,11 @@ def _dtype(tensor: Tensor, what: str) -> int:
         raise RuntimeError(f"qste_b200 {what}: unsupported dtype {tensor.dtype}") from None
 
 
-def _ptr(tensor: Tensor | None):
+def _ptr(tensor: Tensor | None, current: int | None = None):
     """The device address of ``tensor``.  Every pointer the library receives goes through here,
     so this is also where a tensor on the host (a module that was converted but never moved to
-    the GPU, say) is refused instead of being handed to a kernel as if it were device memory."""
+    the GPU, say) is refused instead of being handed to a kernel as if it were device memory.
+    ``current``: the current device's index, for callers that looked it up once for the call."""
 
     if tensor is None or tensor.numel() == 0:
         return None
@@ -66,7 +67,8 @@ def _ptr(tensor: Tensor | None):
             f"qste_b200: expected every tensor of the call on the GPU, got one on '{tensor.device}' "
             f"(shape {tuple(tensor.shape)}, {tensor.dtype}); move the converted module with .to(device)."
         )
-    current = torch.cuda.current_device()
+    if current is None:
+        current = torch.cuda.current_device()
     if tensor.device.index is not None and tensor.device.index != current:
         raise RuntimeError(
             f"qste_b200: tensor on cuda:{tensor.device.index} passed while cuda:{current} is the current "
@@ -94,12 +96,13 @@ def _stream(device: torch.device):
 _workspaces: dict[tuple[int, int], Tensor] = {}
 
 
-def _workspace(device: torch.device, nbytes: int) -> Tensor:
-    """A zero-initialised scratch buffer per (device, stream), grown on demand."""
+def _workspace(device: torch.device, nbytes: int, stream: int | None = None) -> Tensor:
+    """A zero-initialised scratch buffer per (device, stream), grown on demand.  ``stream``: the
+    current stream's handle, for callers that looked it up once for the call."""
 
     nbytes = max(int(nbytes), 256)
     key = (device.index if device.index is not None else torch.cuda.current_device(),
-           torch.cuda.current_stream(device).cuda_stream)
+           torch.cuda.current_stream(device).cuda_stream if stream is None else stream)
     held = _workspaces.get(key)
     if held is None or held.numel() < nbytes:
         grown = torch.zeros(nbytes, dtype=torch.uint8, device=device)
@@ -310,12 +313,16 @@ def packed_linear_affine(inputs: Tensor, packed: Tensor, scale: Tensor, bias: Te
     path = _path()
     library = _cabi.load()
     with _on(device):
+        # the current device and stream are looked up once: for a batch of one the host side of this
+        # call costs several times what the kernel takes
+        current = torch.cuda.current_device()
+        stream = torch.cuda.current_stream(device).cuda_stream
         need = library.qste_b200_packed_linear_affine_workspace(samples, rows, columns, code, path)
-        workspace = _workspace(device, need)
+        workspace = _workspace(device, need, stream)
         _cabi.check(library.qste_b200_packed_linear_affine(
-            _ptr(flat), code, samples, _ptr(packed), _ptr(scale32), _ptr(bias32), rows, columns,
-            _ptr(out), code, path, _ptr(workspace), workspace.numel(), _stream(device)),
-            "packed_linear_affine")
+            _ptr(flat, current), code, samples, _ptr(packed, current), _ptr(scale32, current), _ptr(bias32, current),
+            rows, columns, _ptr(out, current), code, path, _ptr(workspace, current), workspace.numel(),
+            ctypes.c_void_p(stream)), "packed_linear_affine")
     return out.view(*inputs.shape[:-1], rows)
 
 
