@@ -58,7 +58,7 @@ typedef enum {
   QSTE_PATH_TENSOR = 2, /* tcgen05/TMEM kernel; QSTE_ERR_UNSUPPORTED when the shape does not fit */
   QSTE_PATH_STREAM = 3  /* the small-batch kernels only (QSTE_ERR_UNSUPPORTED where none applies): forward by look-up
                            tables for 1-2 tokens (1-4 of fp32) or weights expanded in registers for 3-32 tokens of
-                           a 16-bit type; qste_b200_linear_backward_evidence in one launch for 1-32 samples */
+                           a 16-bit type; qste_b200_linear_backward_evidence in one launch for 1-128 samples */
 } qste_path;
 
 int qste_b200_abi_version(void);
@@ -174,8 +174,9 @@ int qste_b200_evidence_from_packed(const void* grad, int dtype, int64_t samples,
  *   evidence   = E0 * weight_scale[r]                       (fp32 [rows, columns])
  *   g_bias[r]  = sum_m dY[m, r]                              (skipped when g_bias is NULL)
  * aux is the saved [2, samples] fp32 tensor: offsets then scales.
- * Batches of 1-32 samples (columns a multiple of 128, at most 16384) run as ONE kernel on the CUDA
- * cores that is bound by writing the result; larger ones on the tensor-core tiles. */
+ * Batches of 1-128 samples (columns a multiple of 128) run as ONE kernel: look-up tables on the CUDA
+ * cores up to 16 samples (fp32 throughout), warp-level MMAs with one fp16 rounding per term above;
+ * larger batches on the tensor-core tiles. */
 size_t qste_b200_linear_backward_evidence_workspace(int64_t samples, int64_t rows,
                                                     int64_t columns, int dtype, int path);
 int qste_b200_linear_backward_evidence(const void* grad, int dtype, int64_t samples, int64_t rows,

@@ -65,10 +65,18 @@ int mma_forward(const void* x, int dtype, int64_t samples, const uint8_t* packed
                 const float* bias, int64_t rows, int64_t columns, void* out, cudaStream_t stream);
 
 // Coordinate evidence (with g_scale and g_bias) for 1..32 samples in one kernel on the CUDA cores,
-// bound by writing the result (evidence_lut.cu).  aux = [offset (M), act_scale (M)].
+// bound by writing the result (evidence_lut.cu; the dispatcher gives it batches up to 16).  aux = [offset (M), act_scale (M)].
 bool evidence_lut_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* grad,
                             const float* evidence);
 int evidence_lut(const void* grad, int dtype, int64_t samples, int64_t rows, const uint8_t* act_bits, const float* aux,
+                 int64_t columns, const uint8_t* weight_bits, const float* weight_scale, float* evidence, float* g_scale,
+                 float* g_bias, cudaStream_t stream);
+
+// The same for 17..128 samples: warp-level MMAs with the activation signs expanded in registers
+// (evidence_mma.cu).
+bool evidence_mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* grad,
+                            const float* evidence);
+int evidence_mma(const void* grad, int dtype, int64_t samples, int64_t rows, const uint8_t* act_bits, const float* aux,
                  int64_t columns, const uint8_t* weight_bits, const float* weight_scale, float* evidence, float* g_scale,
                  float* g_bias, cudaStream_t stream);
 

@@ -22,6 +22,17 @@ inline bool small_batch_auto() {
   return enabled;
 }
 
+// The largest batch whose evidence goes to the look-up-table kernel (exact in fp32, write-bound up to
+// here); above it the MMA kernel is faster.  QSTE_B200_EVIDENCE_TABLES=n (0..32) moves the hand-over.
+inline int evidence_table_samples() {
+  static const int samples = [] {
+    const char* text = getenv("QSTE_B200_EVIDENCE_TABLES");
+    const int value = text ? atoi(text) : 16;
+    return value < 0 ? 0 : (value > 32 ? 32 : value);
+  }();
+  return samples;
+}
+
 }  // namespace
 
 extern "C" {
@@ -184,11 +195,16 @@ int qste_b200_linear_backward_evidence(const void* grad, int dtype, int64_t samp
   if (!evidence && columns > 0) return QSTE_ERR_NULL;
   if (!weight_scale || (columns > 0 && !weight_bits)) return QSTE_ERR_NULL;
   if (samples > 0 && (!grad || !aux || (columns > 0 && !act_bits))) return QSTE_ERR_NULL;
-  // 1..32 samples: one kernel on the CUDA cores, bound by writing the result (evidence_lut.cu)
-  if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) && samples > 0 && columns > 0 &&
-      evidence_lut_supported(samples, rows, columns, dtype, grad, evidence))
-    return evidence_lut(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
-                        g_scale, g_bias, as_stream(stream));
+  // Small batches, one launch each: up to 16 samples on the CUDA cores by look-up tables, exact in fp32
+  // (evidence_lut.cu); 17..128 by warp-level MMAs (evidence_mma.cu)
+  if ((path == QSTE_PATH_STREAM || (path == QSTE_PATH_AUTO && small_batch_auto())) && samples > 0 && columns > 0) {
+    if (samples <= evidence_table_samples() && evidence_lut_supported(samples, rows, columns, dtype, grad, evidence))
+      return evidence_lut(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
+                          g_scale, g_bias, as_stream(stream));
+    if (evidence_mma_supported(samples, rows, columns, dtype, grad, evidence))
+      return evidence_mma(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
+                          g_scale, g_bias, as_stream(stream));
+  }
   if (path == QSTE_PATH_STREAM) return QSTE_ERR_UNSUPPORTED;
   const size_t need = qste_b200_linear_backward_evidence_workspace(samples, rows, columns, dtype, path);
   if (!workspace || workspace_bytes < need) return QSTE_ERR_WORKSPACE;
@@ -299,9 +315,10 @@ int qste_b200_linear_backward_staged(const void* grad, int dtype, int64_t sample
   if (!workspace || workspace_bytes < qste_b200_linear_backward_workspace(samples, rows, columns, dtype))
     return QSTE_ERR_WORKSPACE;
   if (!aligned(workspace, 256)) return QSTE_ERR_ALIGNMENT;
-  // (a batch of up to 32 samples takes the two separate calls: its evidence has a kernel of its own)
+  // (a batch of up to 128 samples takes the two separate calls: its evidence has kernels of its own)
   const bool small = small_batch_auto() && samples > 0 && columns > 0 && grad && evidence &&
-                     evidence_lut_supported(samples, rows, columns, dtype, grad, evidence);
+                     ((samples <= evidence_table_samples() && evidence_lut_supported(samples, rows, columns, dtype, grad, evidence)) ||
+                      evidence_mma_supported(samples, rows, columns, dtype, grad, evidence));
   const bool fused = !small && dtype == QSTE_BF16 && samples > 0 && rows > 0 && columns > 0 && grad && weight_bits &&
                      weight_scale && act_bits && aux && grad_input && evidence &&
                      tc_supported(TC_TRANSPOSE, samples, columns, rows, dtype, grad, weight_bits, grad_input, grad_input_dtype) &&

@@ -384,14 +384,16 @@ def test_tensor_core_evidence(samples, rows, columns, dtype):
     assert kernels.wait_timeouts() == 0
 
 
-@pytest.mark.parametrize("samples", [1, 3, 4, 5, 16, 17, 32])
+@pytest.mark.parametrize("samples", [1, 3, 4, 5, 8, 9, 16, 17, 32, 33, 64, 100, 128])
 @pytest.mark.parametrize("rows,columns", [(5, 128), (97, 256), (515, 1024), (3072, 768), (300, 16384), (4104, 4096)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_small_batch_evidence_kernel(samples, rows, columns, dtype):
-    """evidence_lut.cu against the oracle: evidence, row-scale gradient and bias gradient of batches
-    of 1..32 samples in one launch -- every count of four-sample groups at its edges, row counts
-    that do not divide over the warps, contractions from 128 to 16384 columns.  "stream" forces the
-    kernel (the call fails where it does not apply)."""
+    """evidence_lut.cu (up to 16 samples, fp32 throughout) and evidence_mma.cu (17..128 samples, each
+    term rounded once to fp16 against its row's own power of two) against the oracle: evidence,
+    row-scale gradient and bias gradient in one launch -- every count of four-sample groups and of
+    32-sample words at its edges, row counts that do not divide over the warps or the slabs,
+    contractions from 128 columns to 16384 (four chunks).  "stream" forces the small-batch kernels
+    (the call fails where none applies)."""
 
     x, dy, bits, scale, _ = _problem(samples, rows, columns, dtype, seed=samples + columns)
     act_bits, act_offset, act_scale = kernels.pack_affine_rows(x.to(DEVICE))
@@ -405,13 +407,40 @@ def test_small_batch_evidence_kernel(samples, rows, columns, dtype):
     grad = dy.float().contiguous()
     plain = oracle.evidence_from_packed(grad, host(act_bits), columns, host(act_scale))
     decoded = plain.astype(np.float64) + (grad.double().t().numpy() @ host(act_offset).astype(np.float64))[:, None]
-    assert rel(host(evidence), decoded * scale.double().numpy()[:, None]) <= 1e-5
-    assert rel(host(g_scale), oracle.packed_row_inner(decoded.astype(np.float32), bits, columns)) <= 1e-4
+    bar = 1e-5 if samples <= 16 else 1e-3
+    assert rel(host(evidence), decoded * scale.double().numpy()[:, None]) <= bar
+    assert rel(host(g_scale), oracle.packed_row_inner(decoded.astype(np.float32), bits, columns)) <= max(bar, 1e-4)
     assert rel(host(g_bias), dy.double().sum(0).numpy()) <= 1e-5
+    # row by row as well: every row is scaled by its own power of two, so a row of small gradients
+    # is as accurate as a row of large ones
+    want = decoded * scale.double().numpy()[:, None]
+    row_error = np.linalg.norm(host(evidence) - want, axis=1) / np.maximum(np.linalg.norm(want, axis=1), 1e-30)
+    assert float(row_error.max()) <= 10 * bar
     # the dispatcher's own choice is the same kernel: identical bits
     auto, auto_scale, _ = kernels.linear_backward_evidence(
         dy.to(DEVICE), act_bits, aux, columns, bits.to(DEVICE), scale.to(DEVICE), want_bias=True)
     assert torch.equal(auto, evidence) and torch.equal(auto_scale, g_scale)
+
+
+def test_small_batch_evidence_with_weight_rows_of_very_different_magnitude():
+    """evidence_mma.cu rounds every term to fp16 against ONE power of two per output row: rows whose
+    gradients are 2^-60 of their neighbours' must come back as accurate as those (their row's own
+    relative error, not the matrix's)."""
+
+    samples, rows, columns = 64, 240, 1024
+    x, dy, bits, scale, _ = _problem(samples, rows, columns, torch.bfloat16, seed=11)
+    dy = (dy.float() * torch.pow(2.0, -2.0 * (torch.arange(rows) % 31).float())[None, :]).to(torch.bfloat16)
+    act_bits, act_offset, act_scale = kernels.pack_affine_rows(x.to(DEVICE))
+    aux = torch.stack((act_offset, act_scale))
+    evidence, g_scale, _ = kernels.linear_backward_evidence(dy.to(DEVICE), act_bits, aux, columns, bits.to(DEVICE), scale.to(DEVICE))
+    grad = dy.float().contiguous()
+    plain = oracle.evidence_from_packed(grad, host(act_bits), columns, host(act_scale))
+    decoded = plain.astype(np.float64) + (grad.double().t().numpy() @ host(act_offset).astype(np.float64))[:, None]
+    want = decoded * scale.double().numpy()[:, None]
+    row_error = np.linalg.norm(host(evidence) - want, axis=1) / np.maximum(np.linalg.norm(want, axis=1), 1e-300)
+    assert float(row_error.max()) <= 2e-3
+    inner = oracle.packed_row_inner(decoded.astype(np.float32), bits, columns)
+    assert float(np.max(np.abs(host(g_scale) - inner) / np.maximum(np.linalg.norm(decoded, axis=1), 1e-300))) <= 2e-3
 
 
 def test_whole_backward_with_rows_of_very_different_magnitude():
