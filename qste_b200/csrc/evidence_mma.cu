@@ -144,26 +144,33 @@ evidence_mma_kernel(const __grid_constant__ EvMmaParams p) {
   for (long long chunk0 = 0; chunk0 < p.K; chunk0 += kEvChunk) {
     const int chunk_columns = (int)((p.K - chunk0) < kEvChunk ? (p.K - chunk0) : kEvChunk);
     __syncthreads();            // the previous chunk's planes are done with (and the staging, first time round)
-    // -- pattern planes of the chunk: an item is eight samples x eight columns, one 8 x 8 transpose
+    // -- pattern planes of the chunk: an item is eight samples x 32 columns -- eight 4-byte loads (all
+    //    in flight together: the build is a chain of trips to L2 otherwise), four 8 x 8 transposes
     {
-      const int byte_columns = chunk_columns / 8;
-      const int items = byte_columns * (kSamples / 8);
+      const int quads = chunk_columns / 32;                      // runs of four byte columns
+      const int items = quads * (kSamples / 8);
+      const uint8_t* bits0 = p.act_bits + (chunk0 >> 3);
       for (int item = threadIdx.x; item < items; item += blockDim.x) {
-        const int group = item % (kSamples / 8), byte_column = item / (kSamples / 8);   // group: eight samples
-        unsigned long long z = 0;
+        const int group = item % (kSamples / 8), quad = item / (kSamples / 8);   // group: eight samples
+        uint32_t rows8[8];
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
           const int m = group * 8 + s;
-          const unsigned long long bits = m < p.M ? p.act_bits[(long long)m * p.pitch + (chunk0 >> 3) + byte_column] : 0u;
-          z |= bits << (8 * s);
+          rows8[s] = m < p.M ? __ldg(reinterpret_cast<const uint32_t*>(bits0 + (long long)m * p.pitch) + quad) : 0u;
         }
-        // bit (8 s + j) -> bit (8 j + s)
-        unsigned long long t = (z ^ (z >> 7)) & 0x00AA00AA00AA00AAull;  z ^= t ^ (t << 7);
-        t = (z ^ (z >> 14)) & 0x0000CCCC0000CCCCull;                    z ^= t ^ (t << 14);
-        t = (z ^ (z >> 28)) & 0x00000000F0F0F0F0ull;                    z ^= t ^ (t << 28);
-        unsigned char* plane = reinterpret_cast<unsigned char*>(planes + (size_t)(group >> 2) * kEvPlane + byte_column * 8) + (group & 3);
+        unsigned char* plane = reinterpret_cast<unsigned char*>(planes + (size_t)(group >> 2) * kEvPlane + quad * 32) + (group & 3);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) plane[4 * j] = (unsigned char)(z >> (8 * j));
+        for (int byte = 0; byte < 4; ++byte) {
+          unsigned long long z = 0;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) z |= (unsigned long long)((rows8[s] >> (8 * byte)) & 0xffu) << (8 * s);
+          // bit (8 s + j) -> bit (8 j + s)
+          unsigned long long t = (z ^ (z >> 7)) & 0x00AA00AA00AA00AAull;  z ^= t ^ (t << 7);
+          t = (z ^ (z >> 14)) & 0x0000CCCC0000CCCCull;                    z ^= t ^ (t << 14);
+          t = (z ^ (z >> 28)) & 0x00000000F0F0F0F0ull;                    z ^= t ^ (t << 28);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) plane[4 * (8 * byte + j)] = (unsigned char)(z >> (8 * j));
+        }
       }
     }
     __syncthreads();
@@ -300,10 +307,10 @@ int launch_ev_mma(EvMmaParams params, cudaStream_t stream) {
 }  // namespace
 
 bool evidence_mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* grad,
-                            const float* evidence) {
+                            const void* act_bits, const float* evidence) {
   if (samples < 1 || samples > 128 || rows < 1 || columns < 128 || columns % 128 != 0) return false;
   if (dtype_size(dtype) == 0) return false;
-  if (!aligned(evidence, 32) || !aligned(grad, dtype_size(dtype))) return false;
+  if (!aligned(evidence, 32) || !aligned(grad, dtype_size(dtype)) || !aligned(act_bits, 4)) return false;
   if (ceil_div(ceil_div(rows, 16), sm_count()) > kEvMaxSlabs) return false;
   return check_arch() == QSTE_OK;
 }

@@ -75,7 +75,7 @@ int evidence_lut(const void* grad, int dtype, int64_t samples, int64_t rows, con
 // The same for 17..128 samples: warp-level MMAs with the activation signs expanded in registers
 // (evidence_mma.cu).
 bool evidence_mma_supported(int64_t samples, int64_t rows, int64_t columns, int dtype, const void* grad,
-                            const float* evidence);
+                            const void* act_bits, const float* evidence);
 int evidence_mma(const void* grad, int dtype, int64_t samples, int64_t rows, const uint8_t* act_bits, const float* aux,
                  int64_t columns, const uint8_t* weight_bits, const float* weight_scale, float* evidence, float* g_scale,
                  float* g_bias, cudaStream_t stream);

@@ -201,7 +201,7 @@ int qste_b200_linear_backward_evidence(const void* grad, int dtype, int64_t samp
     if (samples <= evidence_table_samples() && evidence_lut_supported(samples, rows, columns, dtype, grad, evidence))
       return evidence_lut(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
                           g_scale, g_bias, as_stream(stream));
-    if (evidence_mma_supported(samples, rows, columns, dtype, grad, evidence))
+    if (evidence_mma_supported(samples, rows, columns, dtype, grad, act_bits, evidence))
       return evidence_mma(grad, dtype, samples, rows, act_bits, aux, columns, weight_bits, weight_scale, evidence,
                           g_scale, g_bias, as_stream(stream));
   }
@@ -318,7 +318,7 @@ int qste_b200_linear_backward_staged(const void* grad, int dtype, int64_t sample
   // (a batch of up to 128 samples takes the two separate calls: its evidence has kernels of its own)
   const bool small = small_batch_auto() && samples > 0 && columns > 0 && grad && evidence &&
                      ((samples <= evidence_table_samples() && evidence_lut_supported(samples, rows, columns, dtype, grad, evidence)) ||
-                      evidence_mma_supported(samples, rows, columns, dtype, grad, evidence));
+                      evidence_mma_supported(samples, rows, columns, dtype, grad, act_bits, evidence));
   const bool fused = !small && dtype == QSTE_BF16 && samples > 0 && rows > 0 && columns > 0 && grad && weight_bits &&
                      weight_scale && act_bits && aux && grad_input && evidence &&
                      tc_supported(TC_TRANSPOSE, samples, columns, rows, dtype, grad, weight_bits, grad_input, grad_input_dtype) &&
