@@ -26,7 +26,7 @@
 //     bytes, a warp's store instruction touches 8 lines instead of 32;
 //   * a CTA owns a few slabs of 16 rows and walks the columns in chunks of 4096; its warps share
 //     out the 32-column blocks of a chunk, so every warp works whatever the row count;
-//   * offset term, bias gradient and exponents come from the staging pass (one thread per row,
+//   * offset term, bias gradient and exponents come from the staging pass (four threads per row,
 //     fp32); g_scale is summed per lane, then over the quad and over the warps in a fixed order.
 //
 // No workspace, no atomics, one launch.
@@ -103,30 +103,46 @@ evidence_mma_kernel(const __grid_constant__ EvMmaParams p) {
   const long long row0 = (long long)blockIdx.x * rows_cta;
   const T* dy = static_cast<const T*>(p.dy);
 
-  // -- staging: one thread per row.  Largest term, offset term and bias gradient in fp32, then
-  //    the row as fp16 in the MMA's sample order, scaled by the row's power of two.
-  for (int r = threadIdx.x; r < rows_cta; r += blockDim.x) {
+  // -- staging: four threads per row, each a quarter of the samples (the loads of a thread are a
+  //    chain of trips to L2, so the chain is what has to be short).  Largest term, offset term and
+  //    bias gradient in fp32, then the row as fp16 in the MMA's sample order, scaled by the row's
+  //    power of two.
+  for (int r0 = 0; r0 < rows_cta; r0 += kEvThreads / 4) {
+    const int r = r0 + (threadIdx.x >> 2), part = threadIdx.x & 3;
     const long long n = row0 + r;
+    const bool live = r < rows_cta && n < p.N;
     float largest = 0.0f, add = 0.0f, bias = 0.0f;
-    if (n < p.N) {
-      for (int m = 0; m < (int)p.M; ++m) {
+    if (live) {
+#pragma unroll 4
+      for (int m = part; m < (int)p.M; m += 4) {
         const float gradient = DType<T>::load(dy + (long long)m * p.N + n);
         largest = fmaxf(largest, fabsf(gradient * p.act_scale[m]));
         add = fmaf(gradient, p.offset[m], add);
         bias += gradient;
       }
-      if (p.g_bias) p.g_bias[n] = bias;
+    }
+#pragma unroll
+    for (int offset = 1; offset <= 2; offset <<= 1) {
+      largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
+      add += __shfl_xor_sync(0xffffffffu, add, offset);
+      bias += __shfl_xor_sync(0xffffffffu, bias, offset);
     }
     int exponent = 0;
     if (largest > 0.0f) frexpf(largest, &exponent);       // largest = f * 2^exponent, f in [0.5, 1)
     const float up = largest > 0.0f ? scalbnf(1.0f, 14 - exponent) : 1.0f;
-    unscale[r] = largest > 0.0f ? scalbnf(1.0f, exponent - 14) : 1.0f;
-    correction[r] = add;
-    __half* row = reinterpret_cast<__half*>(a_rows + (size_t)r * kAPitch);
-    for (int m = 0; m < kSamples; ++m) {
-      float value = 0.0f;
-      if (n < p.N && m < p.M) value = DType<T>::load(dy + (long long)m * p.N + n) * p.act_scale[m] * up;
-      row[(m & ~31) + ev_position(m & 31)] = __float2half_rn(value);
+    if (r < rows_cta) {
+      if (part == 0) {
+        if (live && p.g_bias) p.g_bias[n] = bias;
+        unscale[r] = largest > 0.0f ? scalbnf(1.0f, exponent - 14) : 1.0f;
+        correction[r] = add;
+      }
+      __half* row = reinterpret_cast<__half*>(a_rows + (size_t)r * kAPitch);
+#pragma unroll 4
+      for (int m = part; m < kSamples; m += 4) {
+        float value = 0.0f;
+        if (live && m < p.M) value = DType<T>::load(dy + (long long)m * p.N + n) * p.act_scale[m] * up;
+        row[(m & ~31) + ev_position(m & 31)] = __float2half_rn(value);
+      }
     }
   }
 
